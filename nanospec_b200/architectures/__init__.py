@@ -1,3 +1,3 @@
-from . import dezolorn, llama, sorizen  # registers Dezolorn, LlamaForCausalLM and Sorizen
+from . import debuvik, dezolorn, llama, sorizen  # registers Debuvik, Dezolorn, LlamaForCausalLM and Sorizen
 
-__all__ = ["dezolorn", "llama", "sorizen"]
+__all__ = ["debuvik", "dezolorn", "llama", "sorizen"]

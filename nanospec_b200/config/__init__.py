@@ -1,4 +1,5 @@
 from .files import ConfigError, read_config_files
+from .debuvik import DebuvikConfig
 from .dezolorn import DezolornConfig
 from .sorizen import SorizenConfig
 from .llama import Llama3RopeScaling, LlamaConfig
@@ -7,7 +8,7 @@ from .registry import Architecture, register_architecture, registered_architectu
 from .engine import EngineConfig
 
 __all__ = [
-    "Architecture", "ConfigError", "DezolornConfig", "EngineConfig", "LayerSpec", "Llama3RopeScaling", "LlamaConfig",
+    "Architecture", "ConfigError", "DebuvikConfig", "DezolornConfig", "EngineConfig", "LayerSpec", "Llama3RopeScaling", "LlamaConfig",
     "ModelRecipe", "PartSpec", "Run", "SorizenConfig", "read_config_files", "register_architecture",
     "registered_architectures", "resolve_architecture",
 ]

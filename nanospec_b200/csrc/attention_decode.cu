@@ -30,7 +30,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ qo_indptr, __nv_bfloat16* __restrict__ out, int o_stride,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
-                        int n_splits, int head_tiles, int keep_first, int wide_weights) {
+                        int n_splits, int head_tiles, int keep_first, int wide_weights, int mask_chunk, float softcap) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -53,7 +53,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int kend = pos + 1;
     // With kept first keys behind a window the block counts keys in a virtual range [kstart, kend) in which the kept keys
     // lie directly before the window: a virtual key below win_start is the real key (virtual - gap); see load_kv_tile.
-    const int win_start = (window > 0 && kend - window > 0) ? kend - window : 0;
+    // mask_chunk > 0: the query sees only the keys of its own chunk of that many positions, counted from position 0.
+    int win_start = (window > 0 && kend - window > 0) ? kend - window : 0;
+    if (mask_chunk > 0) win_start = max(win_start, (pos / mask_chunk) * mask_chunk);
     const int gap = win_start - min(keep_first, win_start);
     const int kstart = gap;
     const int chunk = (((kend - kstart + n_splits - 1) / n_splits + kTileKeys - 1) / kTileKeys) * kTileKeys;
@@ -92,6 +94,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     uint32_t qf[D / 16][4];
     const float sl = scale * kLog2e;
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * kLog2e;  // s -> softcap * tanh(s / softcap)
     const int mat = lane >> 3, r8 = lane & 7;
 
     for (int t = 0; t < n_tiles; ++t) {
@@ -127,7 +130,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int key = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
-                    const float v = key < k1 ? s[nb][j] * sl : -INFINITY;
+                    const float v = key >= k1 ? -INFINITY : softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
                     s[nb][j] = v;
                     mx[j >> 1] = fmaxf(mx[j >> 1], v);
                 }
@@ -277,7 +280,8 @@ template <int D, int kStages>
 int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0,
+                  int mask_chunk = 0, float softcap = 0.f) {
     constexpr int S = NsTile<D>::kStride;
     const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
@@ -292,7 +296,7 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
     NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
-        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights);
+        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights, mask_chunk, softcap);
     NS_CHECK_LAUNCH("ns_attention_decode");
     return NS_OK;
 }
@@ -303,14 +307,15 @@ template <int D>
 int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0,
+                  int mask_chunk = 0, float softcap = 0.f) {
     if (g_decode_stages == 2)
         return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                           qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights);
+                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
     return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                       qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights);
+                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
 }
 
 }  // namespace
@@ -337,14 +342,19 @@ NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int
 // (n_tokens of them); without it the tokens are 0 .. n_tokens-1.
 // `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
 // `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
+// `mask_chunk` > 0: a query sees only the keys of its own chunk of that many positions; `softcap` > 0: a scaled score s
+// becomes softcap * tanh(s / softcap).  Kept first keys and chunks do not go together.
 NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_stride, const int* token_req, const int* positions,
                                     const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
                                     int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
-                                    float scale, int window, int keep_first, int wide_weights, int n_splits, cudaStream_t stream) {
+                                    float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap, int n_splits,
+                                    cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
+    if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: mask_chunk=%d with keep_first=%d", mask_chunk, keep_first);
     if (d % 16 || d < 16 || d > 128)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d (multiples of 16 up to 128)", d);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: %d query heads over %d kv heads", nq, nkv);
@@ -355,7 +365,7 @@ NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_c
     case DD:                                                                                                           \
         return launch_decode<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,       \
                                  qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,         \
-                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights);
+                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
     switch (d) {
         NS_DECODE_CASE(16) NS_DECODE_CASE(32) NS_DECODE_CASE(48) NS_DECODE_CASE(64)
         NS_DECODE_CASE(80) NS_DECODE_CASE(96) NS_DECODE_CASE(112) NS_DECODE_CASE(128)
@@ -371,7 +381,7 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
                                float scale, int window, int n_splits, cudaStream_t stream) {
     return ns_attention_decode_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr, out,
                                     o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0, 0,
-                                    n_splits, stream);
+                                    0, 0.f, n_splits, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -8,7 +8,10 @@
 //
 // A query at position p of request r sees the keys at positions max(0, p - window + 1) .. p
 // of the same request (window == 0: all of 0 .. p) and, with keep_first > 0, also the keys at
-// positions 0 .. keep_first - 1 however far back they lie (they keep their own positions).  Keys and
+// positions 0 .. keep_first - 1 however far back they lie (they keep their own positions).  With chunk > 0 the
+// sequence is cut into chunks of that many positions counted from position 0 and a query sees only the keys of its
+// own chunk: the first visible key is then no earlier than floor(p / chunk) * chunk.  With softcap > 0 a score s
+// (after the scale) becomes softcap * tanh(s / softcap) before the softmax.  Keys and
 // values are read from cache[page, kv_head, offset, :] with page = block_table[r, position / page_size];
 // the step's own keys have been written before this kernel runs.  kv_head = q_head / (nq / nkv).
 // Keys have d features and values dv (the two caches are separate tensors).
@@ -24,7 +27,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_req, const int* __restrict__ positions, T* __restrict__ out,
                          int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
-                         int keep_first) {
+                         int keep_first, int chunk, float softcap) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     extern __shared__ float qsm[];
@@ -38,7 +41,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
     const int pos = positions[n];
     const int hk = h / (nq / nkv);
     const int kend = pos + 1;
-    const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) kstart = max(kstart, (pos / chunk) * chunk);
 
     float* qs = qsm + wib * d;
     const T* qrow = q + (size_t)n * q_stride + (size_t)h * d;
@@ -68,6 +72,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
             float dot = 0.f;
             for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ns_ld(kr, e), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float m_new = fmaxf(m, ns_warp_max(s));
         const float corr = expf(m - m_new);  // first chunk: exp(-inf) = 0
@@ -100,7 +105,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
 template <typename T>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int table_stride, const int* token_req, const int* positions, void* out, int o_stride, int n_tokens, int nq,
-           int nkv, int d, int dv, int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
+           int nkv, int d, int dv, int page_size, float scale, int window, int keep_first, int chunk, float softcap, cudaStream_t stream) {
     const long long warps = (long long)n_tokens * nq;
     const unsigned blocks = (unsigned)((warps + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
@@ -109,7 +114,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     case D:                                                                                                          \
         NS_LAUNCH((attention_generic_kernel<T, D>), blocks, kWarpsPerBlock * 32, smem, stream,                                \
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride, token_req,       \
-            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first);                           \
+            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap);                           \
         break;
     switch (dpl) {
         NS_ATTN_CASE(1) NS_ATTN_CASE(2) NS_ATTN_CASE(3) NS_ATTN_CASE(4)
@@ -125,17 +130,18 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 NS_API int ns_attention_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* token_req, const int* positions,
                                 void* out, int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size,
-                                float scale, int window, int keep_first, int dtype, cudaStream_t stream) {
+                                float scale, int window, int keep_first, int chunk, float softcap, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (d < 1 || d > 256 || dv < 1 || dv > 256)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: head sizes %d (keys) and %d (values) must lie in 1..256", d, dv);
-    if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: window=%d keep_first=%d", window, keep_first);
+    if (keep_first < 0 || window < 0 || chunk < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: window=%d keep_first=%d chunk=%d", window, keep_first, chunk);
+    if (chunk > 0 && keep_first > 0) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: kept first keys and chunks do not go together");
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: %d query heads over %d kv heads", nq, nkv);
     if (dtype == NS_F32)
         return launch<float>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, out,
-                             o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, stream);
+                             o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, stream);
     if (dtype == NS_BF16)
         return launch<__nv_bfloat16>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
-                                     out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, stream);
+                                     out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, stream);
     NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: unknown dtype %d", dtype);
 }

@@ -9,7 +9,9 @@
 // (m16n8k16), the softmax is online in fp32 (base 2).  A query at position p sees keys
 // max(0, p - window + 1) .. p (window 0: all of 0 .. p) and, with keep_first > 0, the keys 0 .. keep_first - 1 as
 // well: the block then counts keys in a virtual range in which the kept keys lie directly before the first row's
-// window (see load_kv_tile) and masks by the real key.
+// window (see load_kv_tile) and masks by the real key.  With mask_chunk > 0 a query sees only the keys of its own
+// chunk of that many positions (chunks counted from position 0): the first visible key is no earlier than
+// floor(p / mask_chunk) * mask_chunk.  With softcap > 0 a scaled score s becomes softcap * tanh(s / softcap).
 //
 // Requests that bring exactly one token are left to the decode kernel; the host lists no tile
 // for them.
@@ -26,7 +28,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
-                         int page_size, float scale, int window, int keep_first, int wide_weights) {
+                         int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -43,7 +45,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int pos0 = positions[tok0];                         // positions of a request's tokens are consecutive
     const int pos_last = pos0 + rows - 1;
     const int kend = pos_last + 1;
-    const int win_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;  // first key of the first row's window
+    int win_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;  // first key of the first row's window
+    if (mask_chunk > 0) win_first = max(win_first, (pos0 / mask_chunk) * mask_chunk);  // ... or of its chunk
     const int gap = win_first - min(keep_first, win_first);  // real keys that the virtual range leaves out before the window
     const int kfirst = gap;                                   // first virtual key
     const int k_begin = gap < win_first ? kfirst : (kfirst / kTileKeys) * kTileKeys;
@@ -77,6 +80,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     int prow[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) prow[i] = pos0 + min(warp * 16 + (lane >> 2) + 8 * i, rows - 1);
+    int cfirst[2] = {0, 0};  // first key of each row's chunk
+    if (mask_chunk > 0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) cfirst[i] = (prow[i] / mask_chunk) * mask_chunk;
+    }
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * kLog2e;
     const int warp_pos_max = pos0 + min(warp * 16 + 15, rows - 1);
     const bool warp_active = warp * 16 < rows;
 
@@ -116,13 +125,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             float mx[2] = {-INFINITY, -INFINITY};
             // tiles that lie wholly inside every row's visible range need no mask
             const int warp_pos_min = pos0 + min(warp * 16, rows - 1);
-            const bool full = kb + kTileKeys - 1 <= warp_pos_min && (window <= 0 || kb > warp_pos_max - window) && kb >= win_first;
+            const bool full = kb + kTileKeys - 1 <= warp_pos_min && (window <= 0 || kb > warp_pos_max - window) && kb >= win_first &&
+                              (mask_chunk <= 0 || kb >= (warp_pos_max / mask_chunk) * mask_chunk);
             if (full) {
 #pragma unroll
                 for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float v = s[nb][j] * sl;
+                        const float v = softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
                         s[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }
@@ -134,8 +144,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                         const int vkey = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
                         const int key = vkey >= win_first ? vkey : vkey - gap;
                         const int p = prow[j >> 1];
-                        const bool seen = key <= p && (window <= 0 || key > p - window || key < keep_first) && vkey >= kfirst;
-                        const float v = seen ? s[nb][j] * sl : -INFINITY;
+                        const bool seen = key <= p && (window <= 0 || key > p - window || key < keep_first) && vkey >= kfirst &&
+                                          key >= cfirst[j >> 1];
+                        const float v = !seen ? -INFINITY : softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
                         s[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }
@@ -217,7 +228,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                    int table_stride, const int* positions, const int* qo_indptr, const int* tiles, int n_tiles,
                    void* out, int o_stride, int nq, int nkv, int page_size, float scale, int window,
-                   cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
+                   cudaStream_t stream, int keep_first = 0, int wide_weights = 0, int mask_chunk = 0, float softcap = 0.f) {
     constexpr int S = NsTile<D>::kStride;
     const size_t smem = (size_t)(kTileQ + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -228,7 +239,8 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
     dim3 grid(n_tiles, nq);
     NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first, wide_weights);
+        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first, wide_weights,
+        mask_chunk, softcap);
     NS_CHECK_LAUNCH("ns_attention_prefill");
     return NS_OK;
 }
@@ -239,13 +251,17 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 // tokens of this step, a multiple of 128).  bfloat16 only; head_dim a multiple of 16 up to 128.
 // `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
 // `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
+// `mask_chunk`, `softcap`: see the top of the file (0: off); kept first keys and chunks do not go together.
 NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                      const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
                                      const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
-                                     int page_size, float scale, int window, int keep_first, int wide_weights, cudaStream_t stream) {
+                                     int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap,
+                                     cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
+    if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: mask_chunk=%d with keep_first=%d", mask_chunk, keep_first);
     if (d % 16 || d < 16 || d > 128)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: head_dim=%d (multiples of 16 up to 128)", d);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: %d query heads over %d kv heads", nq, nkv);
@@ -255,7 +271,8 @@ NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_
 #define NS_PREFILL_CASE(DD)                                                                                          \
     case DD:                                                                                                         \
         return launch_prefill<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr,   \
-                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first, wide_weights);
+                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first, wide_weights, \
+                                  mask_chunk, softcap);
     switch (d) {
         NS_PREFILL_CASE(16) NS_PREFILL_CASE(32) NS_PREFILL_CASE(48) NS_PREFILL_CASE(64)
         NS_PREFILL_CASE(80) NS_PREFILL_CASE(96) NS_PREFILL_CASE(112) NS_PREFILL_CASE(128)
@@ -269,5 +286,5 @@ NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache
                                 const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                 int page_size, float scale, int window, cudaStream_t stream) {
     return ns_attention_prefill_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr, tiles, n_tiles,
-                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, stream);
+                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, 0, 0.f, stream);
 }

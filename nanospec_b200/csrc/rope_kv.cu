@@ -221,7 +221,8 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
 //   pairing: interleaved = 1 turns (2i, 2i+1), 0 turns (i, i + rot_pairs)
 //   angle = float(position) * inv_freq[i]; cos and sin are multiplied by `magnitude`
 // A row of `qkv` is [q: nq*d | k: nkv*d | v: nkv*dv]; q and k are rewritten in place, k and v go to
-// cache[page, kv head, offset, :] (keys d wide, values dv wide) when write_kv.  One block per token;
+// cache[page, kv head, offset, :] (keys d wide, values dv wide) when write_kv.  `bias` (optional, float, laid out like
+// the row) is the projections' bias: it is added before the norm, and v is stored with it.  One block per token;
 // everything is computed in float and rounded once.
 // ---------------------------------------------------------------------------------------
 namespace {
@@ -233,7 +234,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
                           const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_pairs,
                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
                           T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d, int dv,
-                          int write_kv) {
+                          int write_kv, const float* __restrict__ bias) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
     const int n = blockIdx.x;
@@ -250,6 +251,12 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
             for (int c = threadIdx.x; c < (q_size + k_size) / 8; c += blockDim.x) {
                 float x[8];
                 ld8(row + c * 8, x);
+                if (bias) {
+                    float b[8];
+                    ld8(bias + c * 8, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] += b[i];
+                }
                 float t = 0.f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t += x[i] * x[i];
@@ -257,7 +264,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
             }
         } else {
             for (int e = threadIdx.x; e < q_size + k_size; e += blockDim.x) {
-                const float x = ns_ld(row, e);
+                const float x = ns_ld(row, e) + (bias ? bias[e] : 0.f);
                 if (e < q_size) ssq += x * x; else ssk += x * x;
             }
         }
@@ -281,7 +288,8 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
     // 16-byte accesses: eight features at a time, when heads, the rotated part and the rows allow it
     const bool vec = d % 8 == 0 && (2 * rot_pairs) % 8 == 0 && (interleaved || rot_pairs % 8 == 0) && row_stride % 8 == 0 &&
                      (uintptr_t)qkv % 16 == 0 && (!write_kv || (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0 && dv % 8 == 0)) &&
-                     (!q_gain || (uintptr_t)q_gain % 16 == 0) && (!k_gain || (uintptr_t)k_gain % 16 == 0);
+                     (!q_gain || (uintptr_t)q_gain % 16 == 0) && (!k_gain || (uintptr_t)k_gain % 16 == 0) &&
+                     (!bias || (uintptr_t)bias % 16 == 0);
     if (vec) {
         // per head: the rotated part in pieces of 8 features (interleaved) or of 8 pairs (two pieces half the part apart), then the rest
         const int rot_items = interleaved ? rot_pairs / 4 : rot_pairs / 8;
@@ -298,18 +306,30 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
                 const int e = 2 * rot_pairs + (it - rot_items) * 8;
                 float x[8];
                 ld8(row + base + e, x);
+                if (bias) {
+                    float b[8];
+                    ld8(bias + base + e, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] += b[i];
+                }
                 if (gain) {
                     float g[8];
                     ld8(gain + goff + e, g);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * g[i];
-                    st8(row + base + e, x);
                 }
+                if (gain || bias) st8(row + base + e, x);
                 if (kc) st8(kc + e, x);
             } else if (interleaved) {
                 const int e = it * 8;
                 float x[8];
                 ld8(row + base + e, x);
+                if (bias) {
+                    float b[8];
+                    ld8(bias + base + e, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] += b[i];
+                }
                 if (gain) {
                     float g[8];
                     ld8(gain + goff + e, g);
@@ -332,6 +352,15 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
                 float lo[8], hi[8];
                 ld8(row + base + e, lo);
                 ld8(row + base + e + rot_pairs, hi);
+                if (bias) {
+                    float b[8];
+                    ld8(bias + base + e, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) lo[i] += b[i];
+                    ld8(bias + base + e + rot_pairs, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) hi[i] += b[i];
+                }
                 if (gain) {
                     float g[8];
                     ld8(gain + goff + e, g);
@@ -361,6 +390,12 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
                 const int h = (w * 8) / dv, e = w * 8 - h * dv;
                 float x[8];
                 ld8(v + w * 8, x);
+                if (bias) {
+                    float b[8];
+                    ld8(bias + q_size + k_size + w * 8, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] += b[i];
+                }
                 st8(v_cache + (slot + (size_t)h * page_size) * dv + e, x);
             }
         }
@@ -378,6 +413,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
         if (u < rot_pairs) {
             const int e0 = interleaved ? 2 * u : u, e1 = interleaved ? 2 * u + 1 : u + rot_pairs;
             float a = ns_ld(row, base + e0), b = ns_ld(row, base + e1);
+            if (bias) { a += bias[base + e0]; b += bias[base + e1]; }
             if (gain) { a = a * inv * gain[goff + e0]; b = b * inv * gain[goff + e1]; }
             float sn, cs;
             sincosf(fpos * inv_freq[u], &sn, &cs);
@@ -388,6 +424,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
         } else {
             const int e = 2 * rot_pairs + (u - rot_pairs);
             float a = ns_ld(row, base + e);
+            if (bias) a += bias[base + e];
             if (gain) a = a * inv * gain[goff + e];
             ns_st(row, base + e, a);
             if (kc) ns_st(kc, e, a);
@@ -397,7 +434,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
         const T* v = row + q_size + k_size;
         for (int w = threadIdx.x; w < nkv * dv; w += blockDim.x) {
             const int h = w / dv, e = w - h * dv;
-            v_cache[(slot + (size_t)h * page_size) * dv + e] = v[w];
+            ns_st(v_cache, (slot + (size_t)h * page_size) * dv + e, ns_ld(v, w) + (bias ? bias[q_size + k_size + w] : 0.f));
         }
     }
 }
@@ -408,7 +445,7 @@ NS_API int ns_qk_norm_rope_store(void* qkv, int row_stride, const int* positions
                                  int table_stride, const float* inv_freq, float magnitude, int interleaved, int rot_pairs,
                                  const float* q_gain, const float* k_gain, float eps, void* k_cache, void* v_cache,
                                  int page_size, int nq, int nkv, int d, int dv, int n_tokens, int write_kv, int dtype,
-                                 cudaStream_t stream) {
+                                 const float* bias, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (rot_pairs < 0 || 2 * rot_pairs > d) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_qk_norm_rope_store: %d pairs in a head of %d", rot_pairs, d);
     if (rot_pairs > 0 && !inv_freq) NS_FAIL(NS_ERR_ARGUMENT, "ns_qk_norm_rope_store: no frequencies");
@@ -416,11 +453,11 @@ NS_API int ns_qk_norm_rope_store(void* qkv, int row_stride, const int* positions
     if (dtype == NS_F32)
         NS_LAUNCH((qk_norm_rope_store_kernel<float>), n_tokens, 256, 0, stream, (float*)qkv, row_stride, positions, token_req,
                   block_table, table_stride, inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, eps, (float*)k_cache,
-                  (float*)v_cache, page_size, nq, nkv, d, dv, write_kv);
+                  (float*)v_cache, page_size, nq, nkv, d, dv, write_kv, bias);
     else if (dtype == NS_BF16)
         NS_LAUNCH((qk_norm_rope_store_kernel<__nv_bfloat16>), n_tokens, 256, 0, stream, (__nv_bfloat16*)qkv, row_stride, positions,
                   token_req, block_table, table_stride, inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, eps,
-                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, dv, write_kv);
+                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, dv, write_kv, bias);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_qk_norm_rope_store: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_qk_norm_rope_store");

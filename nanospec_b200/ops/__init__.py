@@ -434,10 +434,12 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: t
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       token_req: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, nq: int, nkv: int,
                       head_dim: int, page_size: int, scale: float | None = None, window: int = 0,
-                      keep_first: int = 0, v_dim: int | None = None) -> torch.Tensor:
+                      keep_first: int = 0, v_dim: int | None = None, chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """q: [N, >= nq*head_dim] rows (a view into the packed projection is fine, unit inner
     stride); out: [N, nq*v_dim] (`v_dim`: the values' head size when it differs from the keys').  `keep_first`: the
-    first so many keys of a request stay visible behind the window.  See csrc/attention_generic.cu for the masking rule."""
+    first so many keys of a request stay visible behind the window.  `chunk` > 0: a query sees only the keys of its own
+    chunk of that many positions; `softcap` > 0: scaled scores pass through softcap * tanh(s / softcap).  See
+    csrc/attention_generic.cu for the masking rule."""
     _cuda(q, k_cache, v_cache, block_table, token_req, positions, out)
     _i32(positions, "positions"), _i32(token_req, "token_req")
     n = out.shape[0]
@@ -450,7 +452,7 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     lib.call("ns_attention_generic", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(), positions.data_ptr(),
              out.data_ptr(), out.stride(0), n, nq, nkv, head_dim, int(v_dim or head_dim), page_size, float(scale), int(window),
-             int(keep_first), dtype_code(q.dtype), _stream())
+             int(keep_first), int(chunk), float(softcap), dtype_code(q.dtype), _stream())
     return out
 
 
@@ -526,7 +528,8 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
-                     work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0, wide_weights: bool = False) -> None:
+                     work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0, wide_weights: bool = False,
+                     chunk: int = 0, softcap: float = 0.0) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
@@ -538,9 +541,10 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
     head_tiles = -(-(nq // nkv) // 16)
     if window == 0:
         keep_first = 0
-    # (kept first keys behind a window are the cp.async kernel's: the TMA kernel loads whole pages in key order)
+    # (kept first keys behind a window, chunks and capped scores are the cp.async kernel's: the TMA kernel loads whole
+    # pages in key order and knows one mask)
     if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0 \
-            and not keep_first and not wide_weights:
+            and not keep_first and not wide_weights and not chunk and not softcap:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
         if work is not None and window == 0:
             ws = ctx.workspace
@@ -566,6 +570,8 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
         n_splits = max(1, min(n_splits, -(-max_kv_len // 128)))
         if window > 0:  # ... of the keys that are visible
             n_splits = max(1, min(n_splits, -(-min(max_kv_len, window + keep_first) // 128)))
+        if chunk > 0:
+            n_splits = max(1, min(n_splits, -(-min(max_kv_len, chunk) // 128)))
     ws = ctx.workspace
     part_o = ws.get("attn_part_o", n_rows * nq * n_splits, head_dim, torch.float32)
     part_ml = ws.get("attn_part_ml", n_rows * nq * n_splits, 2, torch.float32)
@@ -574,7 +580,7 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
-             int(keep_first), int(bool(wide_weights)), n_splits, _stream())
+             int(keep_first), int(bool(wide_weights)), int(chunk), float(softcap), n_splits, _stream())
 
 
 PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
@@ -582,11 +588,12 @@ PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whateve
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0,
-                      wide_weights: bool = False) -> None:
+                      wide_weights: bool = False, chunk: int = 0, softcap: float = 0.0) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
     if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 and not wide_weights \
+            and not chunk and not softcap \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         # heads of 64: two query heads of a kv head to a block (four softmax warps per sub-partition keep the exponential
         # unit busier and the keys are read once for both) - once one head to a block would give more blocks than SMs
@@ -601,7 +608,7 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
     lib.call("ns_attention_prefill_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
-             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), _stream())
+             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), int(chunk), float(softcap), _stream())
 
 
 def _attention_plan(ctx) -> dict:
@@ -637,20 +644,23 @@ def _attention_plan(ctx) -> dict:
 
 
 def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-              window: int = 0, keep_first: int = 0, v_dim: int | None = None, wide_weights: bool = False) -> torch.Tensor:
+              window: int = 0, keep_first: int = 0, v_dim: int | None = None, wide_weights: bool = False, chunk: int = 0,
+              softcap: float = 0.0) -> torch.Tensor:
     """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
 
     bfloat16 with a head size that the tensor-core kernels take: the decode kernel for requests
     that bring one token, the prefill kernel for the others.  `wide_weights`: the softmax weights meet the values
     with about 16 bits each (two bfloat16 products per weight) instead of 8, for designs that state their weights in
-    float32; the m16n8k16 kernels have it.  float32, and head sizes those
+    float32; the m16n8k16 kernels have it.  `chunk` > 0: a query sees only the keys of its own chunk of that many
+    positions, counted from position 0; `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the exact and
+    the m16n8k16 kernels).  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim
     keep_first = keep_first if window else 0
     if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64 or v_dim != head_dim:
         # (values of another size than the keys are the exact kernel's alone)
         return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
-                                 head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim)
+                                 head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim, chunk, softcap)
     _cuda(qkv, out, lane.k, lane.v, lane.block_table)
     if out.stride(1) != 1 or qkv.stride(1) != 1 or lane.k.dtype != qkv.dtype:
         raise KernelError("attention: row-major bfloat16 operands and a bfloat16 cache are needed")
@@ -665,18 +675,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         fork, join = _side_events(qkv.device)
         fork.record(main)
         side.wait_event(fork)
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap)
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights)
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap)
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights)
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap)
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap)
     return out
 
 
@@ -738,12 +748,16 @@ def scale_softcap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) ->
 
 def qk_norm_rope_store(qkv: torch.Tensor, ctx, lane, inv_freq: torch.Tensor | None, magnitude: float, interleaved: bool,
                        nq: int, nkv: int, head_dim: int, v_dim: int, q_gain: torch.Tensor | None = None,
-                       k_gain: torch.Tensor | None = None, eps: float = 0.0, write_kv: bool = True) -> None:
+                       k_gain: torch.Tensor | None = None, eps: float = 0.0, write_kv: bool = True,
+                       bias: torch.Tensor | None = None) -> None:
     """Rows [q: nq*head_dim | k: nkv*head_dim | v: nkv*v_dim]: an RMS norm of the whole q and of the whole k projection
     (when gains are given), a rotation of the first 2 * len(inv_freq) features of each head (pairs (2i, 2i+1) when
     `interleaved`, (i, i + len) otherwise; cos and sin times `magnitude`), q and k rewritten in place, k and v stored at
-    the tokens' cache slots when `write_kv` (csrc/rope_kv.cu)."""
-    _cuda(qkv, inv_freq, q_gain, k_gain)
+    the tokens' cache slots when `write_kv` (csrc/rope_kv.cu).  `bias` (float32, one entry per feature of the row): the
+    projections' bias, added before the norm.  `nkv` 0: rows of q alone (a mixer that reads another's keys and values)."""
+    _cuda(qkv, inv_freq, q_gain, k_gain, bias)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != nq * head_dim + nkv * (head_dim + v_dim)):
+        raise KernelError("qk_norm_rope_store: a contiguous float32 bias with one entry per feature of [q | k | v]")
     n = qkv.shape[0]
     if qkv.stride(1) != 1 or qkv.shape[1] < nq * head_dim + nkv * (head_dim + v_dim):
         raise KernelError("qk_norm_rope_store: rows of [q | k | v] with unit inner stride")
@@ -760,7 +774,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, ctx, lane, inv_freq: torch.Tensor | No
              _ptr(bt), bt.stride(0) if bt is not None else 0, _ptr(inv_freq), float(magnitude), int(bool(interleaved)),
              inv_freq.numel() if inv_freq is not None else 0, _ptr(q_gain), _ptr(k_gain), float(eps),
              _ptr(lane.k) if write_kv else None, _ptr(lane.v) if write_kv else None, lane.page_size, nq, nkv, head_dim, v_dim, n,
-             int(bool(write_kv)), dtype_code(qkv.dtype), _stream())
+             int(bool(write_kv)), dtype_code(qkv.dtype), _ptr(bias), _stream())
 
 
 def scan_padded_dim(head_dim: int) -> int:
@@ -1087,3 +1101,57 @@ def moe_expert_rows(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     lib.call("ns_moe_expert_rows", x.data_ptr(), ids.data_ptr(), weights.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(),
              w_down.data_ptr(), act.data_ptr(), out.data_ptr(), n, top, width, ff, dtype_code(x.dtype), _stream())
     return out
+
+
+# ---- a norm on a sublayer's output, a token's own gated input, a gate and a bias on rows -------------------------------
+
+def norm_add(resid: torch.Tensor, branch: torch.Tensor | None, gain: torch.Tensor | None, eps: float,
+             cast: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> torch.Tensor | None:
+    """resid += rmsnorm(branch (+ bias)) * gain, statistics in float32, and `cast` (when given) = the updated rows in its
+    own type.  `branch` None: only `cast` is written.  Returns `cast`."""
+    _cuda(resid, branch, gain, cast, bias)
+    n, hidden = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("norm_add: the residual stream is contiguous float32")
+    dt = branch.dtype if branch is not None else cast.dtype if cast is not None else torch.float32
+    if branch is not None and (branch.shape != resid.shape or not branch.is_contiguous() or gain is None
+                               or gain.dtype != torch.float32 or gain.numel() != hidden or not gain.is_contiguous()):
+        raise KernelError("norm_add: a contiguous branch of the stream's shape and a float32 gain of its width")
+    if cast is not None and (cast.shape != resid.shape or not cast.is_contiguous() or cast.dtype != dt):
+        raise KernelError("norm_add: the copy must be contiguous, of the stream's shape and the branch's dtype")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != hidden or not bias.is_contiguous()):
+        raise KernelError("norm_add: a float32 bias of the stream's width")
+    lib.call("ns_norm_add", resid.data_ptr(), _ptr(branch), _ptr(bias), _ptr(gain), _ptr(cast), n, hidden, float(eps), dtype_code(dt),
+             _stream())
+    return cast
+
+
+def token_gate(a: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, offset: int, out: torch.Tensor) -> torch.Tensor:
+    """out[n, j] = gelu_tanh(a[n, j]) * table[ids[n], offset + j]; a padding row (a negative id) gives zeros."""
+    _cuda(a, table, ids, out)
+    _i32(ids, "ids")
+    n, dim = out.shape
+    if a.shape != (n, dim) or a.stride(1) != 1 or table.stride(1) != 1 or not out.is_contiguous() or ids.numel() != n \
+            or a.dtype != out.dtype or table.dtype != out.dtype or offset < 0 or offset + dim > table.shape[1]:
+        raise KernelError("token_gate: a and out [N, dim] and a table of one dtype whose rows hold offset + dim columns")
+    lib.call("ns_token_gate", a.data_ptr(), a.stride(0), table.data_ptr(), table.stride(0), ids.data_ptr(), table.shape[0],
+             int(offset), out.data_ptr(), n, dim, dtype_code(out.dtype), _stream())
+    return out
+
+
+def sigmoid_mul(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x *= sigmoid(gate), in place; both [N, C] with unit inner strides (the gate may be a column range of a projection)."""
+    _cuda(x, gate)
+    if x.shape != gate.shape or x.dim() != 2 or x.stride(1) != 1 or gate.stride(1) != 1 or x.dtype != gate.dtype:
+        raise KernelError("sigmoid_mul: rows of one shape and dtype with unit inner strides")
+    lib.call("ns_sigmoid_mul", x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), x.shape[0], x.shape[1], dtype_code(x.dtype), _stream())
+    return x
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[n, c] += bias[c], in place; `bias` float32."""
+    _cuda(x, bias)
+    if x.dim() != 2 or x.stride(1) != 1 or bias.dtype != torch.float32 or bias.numel() != x.shape[1] or not bias.is_contiguous():
+        raise KernelError("add_bias: rows with a unit inner stride and a float32 bias of their width")
+    lib.call("ns_add_bias", x.data_ptr(), x.stride(0), bias.data_ptr(), x.shape[0], x.shape[1], dtype_code(x.dtype), _stream())
+    return x

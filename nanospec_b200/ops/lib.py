@@ -29,10 +29,10 @@ _SIGNATURES: dict[str, list] = {
     "ns_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "ns_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "ns_rope_kv_write": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "ns_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ns_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _I, _P],
     "ns_add_layernorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "ns_scale_softcap": [_P, _I, _I, _L, _F, _F, _P],
-    "ns_qk_norm_rope_store": [_P, _I, _P, _P, _P, _I, _P, _F, _I, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ns_qk_norm_rope_store": [_P, _I, _P, _P, _P, _I, _P, _F, _I, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ns_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "ns_rotary_prepare": [_P, _I, _P, _P, _P, _F, _I, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "ns_linear_scan": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -50,8 +50,8 @@ _SIGNATURES: dict[str, list] = {
     "ns_gemm_bf16_tc_gated": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ns_attention_prefill_tc": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "ns_wait_probe": [_P, _L, _P, _P],
-    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
-    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _I, _P],
+    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _P],
     "ns_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "ns_stream_mix_norm": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
     "ns_stream_read": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -69,6 +69,10 @@ _SIGNATURES: dict[str, list] = {
     "ns_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_expert_rows": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "ns_activation": [_P, _P, _L, _I, _I, _P],
+    "ns_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
+    "ns_token_gate": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _I, _I, _P],
+    "ns_sigmoid_mul": [_P, _L, _P, _L, _I, _I, _I, _P],
+    "ns_add_bias": [_P, _L, _P, _I, _I, _I, _P],
 }
 
 

@@ -19,12 +19,21 @@ Interface of a block part (built from a whole `LayerSpec`):
     input_norm_sink(resid, ctx) -> ops.NormSink or None   (optional; None or absent: the block's first norm cannot be folded)
 The built-in mixers and feed-forwards return their result in the step's "branch" buffer: an arrangement that needs
 two branch outputs at once copies the first before it runs the second.
+
+"outnorm" norms what a sublayer returns instead of what it reads: x = x + norm(mixer(x)); x = x + norm(feed_forward(x)),
+then, when the layer has one, x = x + norm(side_input(x)) (`LayerSpec.params["side_input"]`, a `PartSpec` of the
+"side_input" slot; checkpoint sub-prefix under the slot name "side_input").  The sublayers read the stream itself, so
+nothing stays pending: one kernel (`ops.norm_add`) norms the branch, adds it to the float32 stream and leaves the
+stream's copy in the compute type for the next sublayer; the block hands that copy on as a `StreamCopy`.
 """
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
+from .. import ops
 from ..config.recipe import LayerSpec
 from .context import LaneView, StepContext
 from .registry import build_part, register_part
@@ -86,3 +95,67 @@ class PreNormBlock:
         if sink is not None:
             return resid, self.feed_forward.forward(x, ctx, sink=sink)
         return resid, self.feed_forward.forward(x, ctx)
+
+
+@dataclass
+class StreamCopy:
+    """What an "outnorm" block hands its successor in place of a pending branch: nothing is pending, and `x` is the
+    stream as it stands, in the compute type (in float32 the stream itself)."""
+
+    x: torch.Tensor
+
+
+@register_part("block", "outnorm")
+class OutNormBlock:
+    slots = ("mixer", "norm_mixer", "feed_forward", "norm_feed_forward", "side_input")
+
+    def __init__(self, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
+        self.layer = layer
+        self.dtype = dtype
+        self.mixer = build_part("mixer", layer.mixer, dtype, device)
+        self.norm_mixer = build_part("norm", layer.norm, dtype, device)
+        has_ff = layer.feed_forward is not None
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device) if has_ff else None
+        self.norm_feed_forward = build_part("norm", layer.norm, dtype, device) if has_ff else None
+        side = layer.params.get("side_input")
+        self.side_input = build_part("side_input", side, dtype, device) if side is not None else None
+        for norm in (self.norm_mixer, self.norm_feed_forward):
+            if norm is not None and (not hasattr(norm, "gain") or getattr(norm, "centered", False) or getattr(norm, "bias", None) is not None):
+                raise ValueError("the outnorm arrangement folds its norms into the residual sum: an RMS norm part with `gain` and `eps` is needed")
+
+    def parts(self) -> dict:
+        return {s: getattr(self, s) for s in self.slots if getattr(self, s) is not None}
+
+    def _copy(self, resid: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if self.dtype == torch.float32:
+            return resid
+        return ctx.buffer("stream_copy", resid.shape[1])
+
+    def _join(self, resid: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float, ctx: StepContext) -> torch.Tensor:
+        """resid += norm(y) * gain; returns the stream's copy in the compute type."""
+        x = self._copy(resid, ctx)
+        ops.norm_add(resid, y, gain, eps, cast=None if x is resid else x)
+        return x
+
+    def forward(self, resid: torch.Tensor, pending, ctx: StepContext, lane: LaneView, writes: bool = True):
+        if isinstance(pending, StreamCopy):
+            x = pending.x
+        else:
+            if pending is not None:  # a block of another kind ran before: its branch joins the stream as it is
+                if not isinstance(pending, torch.Tensor):
+                    raise ValueError("the outnorm arrangement follows a block that leaves a tensor, or one of its own kind")
+                ops.residual_add(resid, pending)
+            x = self._copy(resid, ctx)
+            if x is not resid:
+                ops.norm_add(resid, None, None, 0.0, cast=x)
+        x = self._join(resid, self.mixer.forward(x, ctx, lane, writes), self.norm_mixer.gain, self.norm_mixer.eps, ctx)
+        if self.feed_forward is not None:
+            x = self._join(resid, self.feed_forward.forward(x, ctx), self.norm_feed_forward.gain, self.norm_feed_forward.eps, ctx)
+        if self.side_input is not None:
+            x = self._join(resid, self.side_input.forward(x, ctx), self.side_input.gain, self.side_input.eps, ctx)
+        return resid, StreamCopy(x)
+
+    def close(self, resid: torch.Tensor, pending, norm, ctx: StepContext, rows: torch.Tensor | None = None,
+              out_name: str = "final_normed") -> torch.Tensor:
+        """The model's end: nothing is pending, the final norm reads the stream; only `rows` when given."""
+        return norm.add_norm(resid, None, ctx, rows=rows, out_name=out_name)

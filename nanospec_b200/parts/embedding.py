@@ -16,7 +16,9 @@ from .registry import register_part
 class TokenEmbedding(Part):
     """params: vocab, hidden, weight_name (the table's name after the part's prefix; default "weight"), scale (the rows
     are multiplied by it; default 1) and copies (the stream is opened as so many equal copies side by side in a row,
-    for a block arrangement that keeps several; default 1)."""
+    for a block arrangement that keeps several; default 1).  side_name and side_columns (optional): a second table
+    [vocab, side_columns] under that name, whose row of a token the layers read slices of (`ctx.extras["token_side"]`
+    is the table; a layer indexes it with the step's token ids on the device, so nothing is gathered here)."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
@@ -24,15 +26,25 @@ class TokenEmbedding(Part):
         self.weight_name = spec.params.get("weight_name", "weight")
         self.scale = float(spec.params.get("scale") or 1.0)
         self.copies = int(spec.params.get("copies") or 1)
+        self.side_name = spec.params.get("side_name")
+        self.side_columns = int(spec.params.get("side_columns") or 0)
         self.table: torch.Tensor | None = None
+        self.side_table: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
-        return {self.weight_name: WeightSpec((self.vocab, self.hidden))}
+        specs = {self.weight_name: WeightSpec((self.vocab, self.hidden))}
+        if self.side_name:
+            specs[self.side_name] = WeightSpec((self.vocab, self.side_columns), std=1.0)
+        return specs
 
     def bind(self, tensors) -> None:
         self.table = tensors[self.weight_name].contiguous()
+        if self.side_name:
+            self.side_table = tensors[self.side_name].contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.side_table is not None:
+            ctx.extras["token_side"] = self.side_table
         if self.scale != 1.0 or self.copies != 1:
             return ops.embed_streams(self.table, ctx.token_ids, ctx.buffer("resid", self.copies * self.hidden, torch.float32),
                                      self.scale, self.copies)

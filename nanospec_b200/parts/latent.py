@@ -6,7 +6,8 @@
     key_h  = [W_uk,h c | kr],  value_h = W_uv,h c
     score  = (q_plain . key_plain + q_rot . kr) * scale,   causal, inside a window when one is set
     softmax, optionally with a learned sink per head in the denominator; optionally head h's output times
-    sigmoid((W_g h)_h); output projection over the heads side by side.
+    sigmoid((W_g h)_h) (gate "head", W_g [heads, hidden]), or every feature of the heads side by side times the sigmoid
+    of its own gate (gate "feature", W_g [heads * v_dim, hidden]); output projection over the heads side by side.
 
 Only [c | kr] is cached (a lane with one key head of rank + rot_dim features and no values).  Keys and values are never
 formed: the plain part of the query is folded through W_uk (q_lat = W_uk,h^T q_plain, a product per head), attention runs
@@ -15,7 +16,7 @@ and the result is unfolded through W_uv,h.  Prompts, portions and single tokens 
 position do not depend on the cut.  The rotation, the latent's norm, scores, softmax and the gate's sigmoid are float32.
 
 params: hidden, heads, dim, rot_dim, v_dim, rank, scale, window (0: every key), eps (of the latent's norm), sink (bool),
-gate (bool), position (a "rotary" PartSpec over rot_dim features, or None), names (optional: tensor names after the
+gate (False, True or "head", or "feature"), position (a "rotary" PartSpec over rot_dim features, or None), names (optional: tensor names after the
 part's prefix, keys "q", "dkv", "dkv_norm", "uk", "uv", "o", "sink", "g").
 """
 
@@ -42,6 +43,10 @@ class LatentAttention(Part):
         self.window = int(p.get("window") or 0)
         self.eps = float(p["eps"])
         self.has_sink, self.has_gate = bool(p.get("sink")), bool(p.get("gate"))
+        self.gate_kind = None if not self.has_gate else "head" if p["gate"] is True else str(p["gate"])
+        if self.gate_kind not in (None, "head", "feature"):
+            raise ValueError(f"latent attention: unknown gate {self.gate_kind!r} (\"head\" or \"feature\")")
+        self.gate_size = 0 if not self.has_gate else self.heads if self.gate_kind == "head" else self.heads * self.v_dim
         self.names = {**_DEFAULT_NAMES, **dict(p.get("names") or {})}
         self.position = build_part("position", p["position"], dtype, device) if p.get("position") is not None else None
         if self.position is not None and (not getattr(self.position, "interleaved", False) or self.position.dims > self.rot_dim):
@@ -64,7 +69,7 @@ class LatentAttention(Part):
         if self.has_sink:
             specs[n["sink"]] = WeightSpec((H,), rule="float32", init="normal", std=1.0)
         if self.has_gate:
-            specs[n["g"]] = WeightSpec((H, self.hidden))
+            specs[n["g"]] = WeightSpec((self.gate_size, self.hidden))
         return specs
 
     def bind(self, tensors) -> None:
@@ -106,7 +111,7 @@ class LatentAttention(Part):
                 ops.linear(q_plain[:, h, :], self.w_uk_t[h], q_lat[h])
         else:
             torch.bmm(q_plain.permute(1, 0, 2), self.w_uk, out=q_lat)
-        gate = proj[:, self.off_gate: self.off_gate + H] if self.has_gate else None
+        gate = proj[:, self.off_gate: self.off_gate + H] if self.gate_kind == "head" else None
         ops.attention_latent(q_lat.permute(1, 0, 2), q_rot, lane, ctx, o_lat.permute(1, 0, 2), self.scale, self.window,
                              self.sink, gate)
         if self.dtype == torch.float32:
@@ -114,4 +119,6 @@ class LatentAttention(Part):
                 ops.linear(o_lat[h], self.w_uv[h], attn[:, h * dv: (h + 1) * dv])
         else:
             torch.bmm(o_lat, self.w_uv.transpose(1, 2), out=attn.view(N, H, dv).permute(1, 0, 2))
+        if self.gate_kind == "feature":
+            ops.sigmoid_mul(attn, proj[:, self.off_gate: self.off_gate + H * dv])
         return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden))

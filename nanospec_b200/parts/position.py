@@ -86,6 +86,15 @@ def rotary_frequencies(dims: int, base: float, scaling: dict | None) -> tuple[to
     if not scaling:
         return f.to(torch.float32), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
+    if "low" in scaling or "high" in scaling:
+        # the wavelength bands (`factor`, `low`, `high`, `original`): with wavelength l = 2 pi / f, a pair with
+        # l < original / high keeps f, one with l > original / low turns `factor` times slower, and between the two
+        # s = (original / l - low) / (high - low) blends them, (1 - s) f / factor + s f; cos and sin are not scaled
+        low, high = float(scaling["low"]), float(scaling["high"])
+        wave = 2.0 * math.pi / f
+        s = (original / wave - low) / (high - low)
+        banded = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, (1.0 - s) * f / factor + s * f))
+        return banded.to(torch.float32), 1.0
 
     def at(turns: float) -> float:
         return dims * math.log(original / (2 * math.pi * turns)) / (2 * math.log(float(base)))
@@ -101,7 +110,8 @@ class Rotary(Part):
     """Rotation of the first `dims` features of every q and k head, in either pairing.
 
     params: head_dim, dims (how many features turn, even, at most head_dim), base, layout ("half": pairs
-    (i, i + dims/2); "interleaved": pairs (2i, 2i + 1)), scaling (None or the YaRN block, see `rotary_frequencies`).
+    (i, i + dims/2); "interleaved": pairs (2i, 2i + 1)), scaling (None, the YaRN block {factor, original, fast, slow} or
+    the wavelength bands {factor, original, low, high}, see `rotary_frequencies`).
     An attention mixer calls `rotate_and_store` (which can also norm the whole q and k projections first and takes
     values of another width than the keys); a mixer with a state reads `inv_freq`, `magnitude` and `interleaved`.
     """
@@ -127,6 +137,8 @@ class Rotary(Part):
         return self._inv_freq
 
     def rotate_and_store(self, qkv: torch.Tensor, ctx: StepContext, lane: LaneView, nq: int, nkv: int, head_dim: int,
-                         writes: bool, v_dim: int | None = None, q_gain=None, k_gain=None, eps: float = 0.0) -> None:
+                         writes: bool, v_dim: int | None = None, q_gain=None, k_gain=None, eps: float = 0.0, bias=None) -> None:
+        """`bias`: the projections' bias, one float32 per feature of the row, added before the norm.  `nkv` 0: the rows
+        hold queries alone (the mixer reads keys and values that another layer stored)."""
         ops.qk_norm_rope_store(qkv, ctx, lane, self.inv_freq if self.dims else None, self.magnitude, self.interleaved, nq, nkv,
-                               head_dim, head_dim if v_dim is None else v_dim, q_gain, k_gain, eps, write_kv=writes)
+                               head_dim, head_dim if v_dim is None else v_dim, q_gain, k_gain, eps, write_kv=writes, bias=bias)

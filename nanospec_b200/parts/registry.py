@@ -10,7 +10,7 @@ import torch
 
 from ..config.recipe import PartSpec
 
-SLOTS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+SLOTS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "side_input")
 _REGISTRY: dict[str, dict[str, Callable]] = {s: {} for s in SLOTS}
 
 
