@@ -16,10 +16,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 // Kept first keys behind a window: the caller counts keys in a virtual range in which the kept keys lie
 // directly before the window; a virtual key below key_split is the real key (virtual - gap).  With
 // gap == 0 virtual and real keys are the same.
+// Keys of dk and values of dv features (multiples of 8, at most D) lie in the cache at their own widths; the tile's columns
+// beyond them are zero-filled, so that the products over D features are those over dk and dv.
 template <int D, int THREADS = kThreads>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const __nv_bfloat16* k_cache,
                                              const __nv_bfloat16* v_cache, const int* bt, int key0, int key_lo, int key_end,
-                                             int hk, int nkv, int page_size, int page_shift, int key_split = 0, int gap = 0) {
+                                             int hk, int nkv, int page_size, int page_shift, int key_split = 0, int gap = 0,
+                                             int dk = D, int dv = D) {
     constexpr int kChunks = D / 8;
     constexpr int kItems = (kTileKeys * kChunks + THREADS - 1) / THREADS;  // 16-byte pieces per thread and tensor
     // When the threads divide evenly over the pieces of a row, a thread keeps the same piece of
@@ -51,13 +54,14 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
         const int vkey = key0 + row;
         const int key = vkey >= key_split ? vkey : vkey - gap;
         const bool valid = page[i] >= 0;
-        size_t off = 0;
+        size_t slot = 0;
         if (valid) {
             const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-            off = (((size_t)page[i] * nkv + hk) * page_size + within) * D + ch * 8;
+            slot = ((size_t)page[i] * nkv + hk) * page_size + within;
         }
-        ns_cp_async16(NsTile<D>::at(ks, row, ch * 8), k_cache + off, valid);
-        ns_cp_async16(NsTile<D>::at(vs, row, ch * 8), v_cache + off, valid);
+        const bool in_k = valid && ch * 8 < dk, in_v = valid && ch * 8 < dv;
+        ns_cp_async16(NsTile<D>::at(ks, row, ch * 8), k_cache + (in_k ? slot * dk + ch * 8 : 0), in_k);
+        ns_cp_async16(NsTile<D>::at(vs, row, ch * 8), v_cache + (in_v ? slot * dv + ch * 8 : 0), in_v);
     }
 }
 

@@ -13,6 +13,10 @@
 // resets the counter.  Launch dimensions do not depend on sequence lengths (they are read from
 // device memory), which lets a decode step be replayed from a CUDA graph.
 //
+// Keys of dk and values of dv features (multiples of 8) run in the instance for D = the larger of the two rounded up to 16:
+// the tiles' columns beyond dk and dv are zero, the products skip the 16-column steps wholly beyond them, and the partial
+// results keep D columns.
+//
 // Tokens whose request brings more than one token to the step are left to the prefill kernel;
 // padding rows (request index < 0) are skipped.
 #include "attention_common.cuh"
@@ -30,7 +34,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ qo_indptr, __nv_bfloat16* __restrict__ out, int o_stride,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
-                        int n_splits, int head_tiles, int keep_first, int wide_weights, int mask_chunk, float softcap) {
+                        int n_splits, int head_tiles, int keep_first, int wide_weights, int mask_chunk, float softcap,
+                        int dk, int dv) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -69,11 +74,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     // ---- q of the group's heads (rows beyond the group are zero) and the first tile ----------
     {
         constexpr int kChunks = D / 8;
-        const __nv_bfloat16* qrow = q + (size_t)n * q_stride + (size_t)h0 * D;
+        const __nv_bfloat16* qrow = q + (size_t)n * q_stride + (size_t)h0 * dk;
         for (int c = tid; c < 16 * kChunks; c += kThreads) {
             const int row = c / kChunks, ch = c - row * kChunks;
-            const bool valid = row < gcount;
-            ns_cp_async16(Tile::at(qs, row, ch * 8), qrow + (valid ? (size_t)row * D + ch * 8 : 0), valid);
+            const bool valid = row < gcount && ch * 8 < dk;
+            ns_cp_async16(Tile::at(qs, row, ch * 8), qrow + (valid ? (size_t)row * dk + ch * 8 : 0), valid);
         }
     }
     // the first kStages-1 tiles are requested up front; every iteration requests one more
@@ -81,7 +86,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     for (int st = 0; st < kStages - 1; ++st) {
         if (st < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)st * 2 * kTileKeys * S;
-            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size, page_shift, win_start, gap);
+            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size, page_shift, win_start, gap, dk, dv);
         }
         ns_cp_async_commit();
     }
@@ -104,7 +109,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (t + kStages - 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + kStages - 1) % kStages) * 2 * kTileKeys * S;
             load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + kStages - 1) * kTileKeys, kstart, k1, hk,
-                            nkv, page_size, page_shift, win_start, gap);
+                            nkv, page_size, page_shift, win_start, gap, dk, dv);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<kStages - 1>();  // tile t has landed; the two after it stay in flight
@@ -119,6 +124,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
+                if (kk * 16 >= dk) break;
                 uint32_t kf[4];
                 ns_ldmatrix_x4(kf, Tile::at(ks, warp * 16 + (mat >> 1) * 8 + r8, kk * 16 + (mat & 1) * 8));
                 ns_mma_bf16(s[0], qf[kk], kf[0], kf[1]);
@@ -168,6 +174,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             }
 #pragma unroll
             for (int nb2 = 0; nb2 < D / 16; ++nb2) {
+                if (nb2 * 16 >= dv) break;
                 uint32_t vf[4];
                 ns_ldmatrix_x4_trans(vf, Tile::at(vs, warp * 16 + (mat & 1) * 8 + r8, nb2 * 16 + (mat >> 1) * 8));
                 ns_mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
@@ -211,6 +218,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     __syncthreads();
     for (int e = tid; e < gcount * D; e += kThreads) {
         const int row = e / D, col = e - row * D;
+        if (col >= dv) continue;
         float mt = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm[w * 16 + row]);
@@ -225,7 +233,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         }
         const int h = h0 + row;
         if (n_splits == 1) {
-            out[(size_t)n * o_stride + (size_t)h * D + col] = __float2bfloat16_rn(acc / lt);
+            out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(acc / lt);
         } else {
             const size_t slot = ((size_t)z * nq + h) * n_splits + split;
             part_o[slot * D + col] = acc;
@@ -251,6 +259,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     __threadfence();
     for (int e = tid; e < gcount * D; e += kThreads) {
         const int row = e / D, col = e - row * D;
+        if (col >= dv) continue;
         const int h = h0 + row;
         const size_t base = ((size_t)z * nq + h) * n_splits;
         // every split's maximum, sum and partial value are requested together, then combined in split order
@@ -272,7 +281,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             acc += os[s2] * f;
             lt += ls[s2] * f;
         }
-        out[(size_t)n * o_stride + (size_t)h * D + col] = __float2bfloat16_rn(acc / lt);
+        out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(acc / lt);
     }
 }
 
@@ -280,8 +289,8 @@ template <int D, int kStages>
 int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0,
-                  int mask_chunk = 0, float softcap = 0.f) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first, int wide_weights,
+                  int mask_chunk, float softcap, int dk, int dv) {
     constexpr int S = NsTile<D>::kStride;
     const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
@@ -296,7 +305,7 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
     NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
-        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights, mask_chunk, softcap);
+        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
     NS_CHECK_LAUNCH("ns_attention_decode");
     return NS_OK;
 }
@@ -307,15 +316,15 @@ template <int D>
 int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0,
-                  int mask_chunk = 0, float softcap = 0.f) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first, int wide_weights,
+                  int mask_chunk, float softcap, int dk, int dv) {
     if (g_decode_stages == 2)
         return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                           qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
+                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
     return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                       qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
+                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
 }
 
 }  // namespace
@@ -344,19 +353,23 @@ NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int
 // `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
 // `mask_chunk` > 0: a query sees only the keys of its own chunk of that many positions; `softcap` > 0: a scaled score s
 // becomes softcap * tanh(s / softcap).  Kept first keys and chunks do not go together.
+// `dv` > 0: values of that many features where the keys have `d` (both multiples of 8 then; the output rows are nq * dv wide
+// and `part_o` holds as many columns per row as the instance that runs: the larger of d and dv rounded up to 16).
 NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_stride, const int* token_req, const int* positions,
                                     const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
                                     int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
                                     float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap, int n_splits,
-                                    cudaStream_t stream) {
+                                    int dv, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
     if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: mask_chunk=%d with keep_first=%d", mask_chunk, keep_first);
-    if (d % 16 || d < 16 || d > 128)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d (multiples of 16 up to 128)", d);
+    if (dv <= 0) dv = d;
+    const int dk = d, dmax = ((d > dv ? d : dv) + 15) / 16 * 16;  // dmax: the instance that runs
+    if (dv == d ? (d % 16 || d < 16 || d > 128) : (d % 8 || dv % 8 || d < 8 || dv < 8 || dmax > 128))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d, values of %d (equal: multiples of 16 up to 128; else of 8)", d, dv);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: %d query heads over %d kv heads", nq, nkv);
     if (n_splits < 1 || n_splits > kMaxSplits) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: n_splits=%d (1..%d)", n_splits, kMaxSplits);
     if (q_stride % 8 || ((uintptr_t)q % 16)) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: q rows must be 16-byte aligned");
@@ -365,8 +378,8 @@ NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_c
     case DD:                                                                                                           \
         return launch_decode<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,       \
                                  qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,         \
-                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap);
-    switch (d) {
+                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
+    switch (dmax) {
         NS_DECODE_CASE(16) NS_DECODE_CASE(32) NS_DECODE_CASE(48) NS_DECODE_CASE(64)
         NS_DECODE_CASE(80) NS_DECODE_CASE(96) NS_DECODE_CASE(112) NS_DECODE_CASE(128)
     }
@@ -381,7 +394,7 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
                                float scale, int window, int n_splits, cudaStream_t stream) {
     return ns_attention_decode_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr, out,
                                     o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0, 0,
-                                    0, 0.f, n_splits, stream);
+                                    0, 0.f, n_splits, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------

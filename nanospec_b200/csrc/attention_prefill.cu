@@ -12,6 +12,8 @@
 // window (see load_kv_tile) and masks by the real key.  With mask_chunk > 0 a query sees only the keys of its own
 // chunk of that many positions (chunks counted from position 0): the first visible key is no earlier than
 // floor(p / mask_chunk) * mask_chunk.  With softcap > 0 a scaled score s becomes softcap * tanh(s / softcap).
+// Keys of dk and values of dv features (multiples of 8) run in the instance for D = the larger of the two rounded up to 16:
+// the tiles' columns beyond dk and dv are zero, and the products skip the 16-column steps that lie wholly beyond them.
 //
 // Requests that bring exactly one token are left to the decode kernel; the host lists no tile
 // for them.
@@ -28,7 +30,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
-                         int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap) {
+                         int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap,
+                         int dk, int dv) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -57,14 +60,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
 
     {
         constexpr int kChunks = D / 8;
-        const __nv_bfloat16* qbase = q + (size_t)tok0 * q_stride + (size_t)h * D;
+        const __nv_bfloat16* qbase = q + (size_t)tok0 * q_stride + (size_t)h * dk;
         for (int c = tid; c < kTileQ * kChunks; c += kPrefillThreads) {
             const int row = c / kChunks, ch = c - row * kChunks;
-            const bool valid = row < rows;
+            const bool valid = row < rows && ch * 8 < dk;
             ns_cp_async16(Tile::at(qs, row, ch * 8), qbase + (valid ? (size_t)row * q_stride + ch * 8 : 0), valid);
         }
     }
-    load_kv_tile<D, kPrefillThreads>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size, page_shift, win_first, gap);
+    load_kv_tile<D, kPrefillThreads>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size, page_shift, win_first, gap, dk, dv);
     ns_cp_async_commit();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -95,7 +98,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         if (t + 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + 1) & 1) * 2 * kTileKeys * S;
             load_kv_tile<D, kPrefillThreads>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k_begin + (t + 1) * kTileKeys, kfirst, kend, hk,
-                            nkv, page_size, page_shift, win_first, gap);
+                            nkv, page_size, page_shift, win_first, gap, dk, dv);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<1>();
@@ -114,6 +117,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 for (int j = 0; j < 4; ++j) s[nb][j] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
+                if (kk * 16 >= dk) break;
 #pragma unroll
                 for (int nb2 = 0; nb2 < 4; ++nb2) {
                     uint32_t kf[4];
@@ -190,6 +194,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 }
 #pragma unroll
                 for (int nb2 = 0; nb2 < D / 16; ++nb2) {
+                    if (nb2 * 16 >= dv) break;
                     uint32_t vf[4];
                     ns_ldmatrix_x4_trans(vf, Tile::at(vs, kb16 * 16 + (mat & 1) * 8 + r8, nb2 * 16 + (mat >> 1) * 8));
                     ns_mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
@@ -215,11 +220,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         const int row = warp * 16 + (lane >> 2) + 8 * i;
         if (row >= rows) continue;
         const float inv = 1.f / l[i];
-        __nv_bfloat16* orow = out + (size_t)(tok0 + row) * o_stride + (size_t)h * D;
+        __nv_bfloat16* orow = out + (size_t)(tok0 + row) * o_stride + (size_t)h * dv;
 #pragma unroll
         for (int nb = 0; nb < D / 8; ++nb) {
             const int col = nb * 8 + 2 * (lane & 3);
-            *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(o[nb][2 * i] * inv, o[nb][2 * i + 1] * inv);
+            if (col < dv) *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(o[nb][2 * i] * inv, o[nb][2 * i + 1] * inv);
         }
     }
 }
@@ -228,7 +233,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                    int table_stride, const int* positions, const int* qo_indptr, const int* tiles, int n_tiles,
                    void* out, int o_stride, int nq, int nkv, int page_size, float scale, int window,
-                   cudaStream_t stream, int keep_first = 0, int wide_weights = 0, int mask_chunk = 0, float softcap = 0.f) {
+                   cudaStream_t stream, int keep_first, int wide_weights, int mask_chunk, float softcap, int dk, int dv) {
     constexpr int S = NsTile<D>::kStride;
     const size_t smem = (size_t)(kTileQ + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -240,7 +245,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
     NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first, wide_weights,
-        mask_chunk, softcap);
+        mask_chunk, softcap, dk, dv);
     NS_CHECK_LAUNCH("ns_attention_prefill");
     return NS_OK;
 }
@@ -252,18 +257,21 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 // `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
 // `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
 // `mask_chunk`, `softcap`: see the top of the file (0: off); kept first keys and chunks do not go together.
+// `dv` > 0: values of that many features where the keys have `d` (both multiples of 8 then, the output rows nq * dv wide).
 NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                      const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
                                      const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                      int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap,
-                                     cudaStream_t stream) {
+                                     int dv, cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
     if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: mask_chunk=%d with keep_first=%d", mask_chunk, keep_first);
-    if (d % 16 || d < 16 || d > 128)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: head_dim=%d (multiples of 16 up to 128)", d);
+    if (dv <= 0) dv = d;
+    const int dmax = ((d > dv ? d : dv) + 15) / 16 * 16;  // the instance that runs
+    if (dv == d ? (d % 16 || d < 16 || d > 128) : (d % 8 || dv % 8 || d < 8 || dv < 8 || dmax > 128))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: head_dim=%d, values of %d (equal: multiples of 16 up to 128; else of 8)", d, dv);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: %d query heads over %d kv heads", nq, nkv);
     if (q_stride % 8 || ((uintptr_t)q % 16) || o_stride % 2)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: q rows must be 16-byte aligned and out rows 4-byte aligned");
@@ -272,8 +280,8 @@ NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_
     case DD:                                                                                                         \
         return launch_prefill<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr,   \
                                   tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first, wide_weights, \
-                                  mask_chunk, softcap);
-    switch (d) {
+                                  mask_chunk, softcap, d, dv);
+    switch (dmax) {
         NS_PREFILL_CASE(16) NS_PREFILL_CASE(32) NS_PREFILL_CASE(48) NS_PREFILL_CASE(64)
         NS_PREFILL_CASE(80) NS_PREFILL_CASE(96) NS_PREFILL_CASE(112) NS_PREFILL_CASE(128)
     }
@@ -286,5 +294,5 @@ NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache
                                 const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                 int page_size, float scale, int window, cudaStream_t stream) {
     return ns_attention_prefill_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr, tiles, n_tiles,
-                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, 0, 0.f, stream);
+                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, 0, 0.f, 0, stream);
 }

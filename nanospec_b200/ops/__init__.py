@@ -506,8 +506,11 @@ def _target_blocks() -> int:
     return 2 * sm_count()
 
 
-def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
-    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+def _tensor_core_attention(dtype: torch.dtype, head_dim: int, v_dim: int | None = None) -> bool:
+    """Keys and values of one width: multiples of 16 up to 128; of two widths: multiples of 8, the larger at most 128."""
+    if v_dim is None or v_dim == head_dim:
+        return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+    return dtype == torch.bfloat16 and head_dim % 8 == 0 and v_dim % 8 == 0 and 8 <= min(head_dim, v_dim) and max(head_dim, v_dim) <= 128
 
 
 USE_CLUSTER_DECODE = True
@@ -529,7 +532,7 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
                      work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0, wide_weights: bool = False,
-                     chunk: int = 0, softcap: float = 0.0) -> None:
+                     chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
@@ -537,14 +540,16 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
     `rows`: int32 device tensor of their token rows, or None when every row of the step is one.
     `work` (int32, four per item, from the cache manager's packer) replaces `rows` for the TMA kernel on lanes without
     a window: a request whose context is much longer than the others' comes as several items, a part of its keys
-    each, and the kernel adds the parts up through `work_slots` slots of scratch."""
+    each, and the kernel adds the parts up through `work_slots` slots of scratch.
+    `v_dim`: values of another width than the keys (both multiples of 8): the cp.async kernel, in its instance for the larger."""
+    v_dim = head_dim if v_dim is None else v_dim
     head_tiles = -(-(nq // nkv) // 16)
     if window == 0:
         keep_first = 0
     # (kept first keys behind a window, chunks and capped scores are the cp.async kernel's: the TMA kernel loads whole
     # pages in key order and knows one mask)
     if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0 \
-            and not keep_first and not wide_weights and not chunk and not softcap:
+            and not keep_first and not wide_weights and not chunk and not softcap and v_dim == head_dim:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
         if work is not None and window == 0:
             ws = ctx.workspace
@@ -573,14 +578,14 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
         if chunk > 0:
             n_splits = max(1, min(n_splits, -(-min(max_kv_len, chunk) // 128)))
     ws = ctx.workspace
-    part_o = ws.get("attn_part_o", n_rows * nq * n_splits, head_dim, torch.float32)
+    part_o = ws.get("attn_part_o", n_rows * nq * n_splits, -(-max(head_dim, v_dim) // 16) * 16, torch.float32)
     part_ml = ws.get("attn_part_ml", n_rows * nq * n_splits, 2, torch.float32)
     counters = ws.get("attn_counters", n_rows * nkv * head_tiles, 1, torch.int32, zero=True)
     lib.call("ns_attention_decode_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
-             int(keep_first), int(bool(wide_weights)), int(chunk), float(softcap), n_splits, _stream())
+             int(keep_first), int(bool(wide_weights)), int(chunk), float(softcap), n_splits, int(v_dim), _stream())
 
 
 PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
@@ -588,12 +593,14 @@ PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whateve
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0,
-                      wide_weights: bool = False, chunk: int = 0, softcap: float = 0.0) -> None:
+                      wide_weights: bool = False, chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
-    on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
+    on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu), also values of
+    another width than the keys (`v_dim`, both multiples of 8)."""
+    v_dim = head_dim if v_dim is None else v_dim
     if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 and not wide_weights \
-            and not chunk and not softcap \
+            and not chunk and not softcap and v_dim == head_dim \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         # heads of 64: two query heads of a kv head to a block (four softmax warps per sub-partition keep the exponential
         # unit busier and the keys are read once for both) - once one head to a block would give more blocks than SMs
@@ -608,7 +615,7 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
     lib.call("ns_attention_prefill_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
-             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), int(chunk), float(softcap), _stream())
+             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), int(chunk), float(softcap), int(v_dim), _stream())
 
 
 def _attention_plan(ctx) -> dict:
@@ -653,12 +660,11 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     with about 16 bits each (two bfloat16 products per weight) instead of 8, for designs that state their weights in
     float32; the m16n8k16 kernels have it.  `chunk` > 0: a query sees only the keys of its own chunk of that many
     positions, counted from position 0; `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the exact and
-    the m16n8k16 kernels).  float32, and head sizes those
+    the m16n8k16 kernels); `v_dim`: values of another width than the keys (the same kernels, widths in multiples of 8).  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim
     keep_first = keep_first if window else 0
-    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64 or v_dim != head_dim:
-        # (values of another size than the keys are the exact kernel's alone)
+    if not _tensor_core_attention(qkv.dtype, head_dim, v_dim) or nq // nkv > 64 or (v_dim != head_dim and (nq * head_dim) % 8):
         return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
                                  head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim, chunk, softcap)
     _cuda(qkv, out, lane.k, lane.v, lane.block_table)
@@ -675,18 +681,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         fork, join = _side_events(qkv.device)
         fork.record(main)
         side.wait_event(fork)
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim)
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap)
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim)
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap)
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim)
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim)
     return out
 
 

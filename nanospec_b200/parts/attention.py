@@ -127,7 +127,14 @@ class GQAAttention(Part):
     def feeds_norm_sink(self, n_tokens: int) -> bool:
         return self.o_bias is None and ops.norm_fusion_ok(n_tokens, self.dtype, self.w_o)
 
-    def forward(self, x, ctx: StepContext, lane: LaneView, writes: bool = True, sink: ops.NormSink | None = None):
+    @property
+    def branch_bias(self) -> torch.Tensor | None:
+        """The output projection's bias: an arrangement that norms the branch in a kernel of its own may call
+        `forward(..., leave_bias=True)` and add this there."""
+        return self.o_bias
+
+    def forward(self, x, ctx: StepContext, lane: LaneView, writes: bool = True, sink: ops.NormSink | None = None,
+                leave_bias: bool = False):
         qkv = ctx.buffer("qkv", self.w_qkv.shape[0])
         if self.general:
             ops.linear(x, self.w_qkv, qkv)
@@ -144,6 +151,8 @@ class GQAAttention(Part):
             attn = ctx.buffer("attn_out", self.o_in)
             ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window,
                           self.keep_first, self.v_dim, self.wide_weights, self.chunk, self.softcap)
+            if self.o_bias is not None and leave_bias:
+                return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden))
             if self.o_bias is not None:
                 return ops.add_bias(ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden)), self.o_bias)
             return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)

@@ -131,10 +131,11 @@ class OutNormBlock:
             return resid
         return ctx.buffer("stream_copy", resid.shape[1])
 
-    def _join(self, resid: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float, ctx: StepContext) -> torch.Tensor:
-        """resid += norm(y) * gain; returns the stream's copy in the compute type."""
+    def _join(self, resid: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float, ctx: StepContext,
+              bias: torch.Tensor | None = None) -> torch.Tensor:
+        """resid += norm(y + bias) * gain; returns the stream's copy in the compute type."""
         x = self._copy(resid, ctx)
-        ops.norm_add(resid, y, gain, eps, cast=None if x is resid else x)
+        ops.norm_add(resid, y, gain, eps, cast=None if x is resid else x, bias=bias)
         return x
 
     def forward(self, resid: torch.Tensor, pending, ctx: StepContext, lane: LaneView, writes: bool = True):
@@ -148,7 +149,10 @@ class OutNormBlock:
             x = self._copy(resid, ctx)
             if x is not resid:
                 ops.norm_add(resid, None, None, 0.0, cast=x)
-        x = self._join(resid, self.mixer.forward(x, ctx, lane, writes), self.norm_mixer.gain, self.norm_mixer.eps, ctx)
+        # a mixer that ends in a bias (`branch_bias`) leaves it to the norm's kernel, which adds it before the statistics
+        bias = getattr(self.mixer, "branch_bias", None)
+        y = self.mixer.forward(x, ctx, lane, writes, leave_bias=True) if bias is not None else self.mixer.forward(x, ctx, lane, writes)
+        x = self._join(resid, y, self.norm_mixer.gain, self.norm_mixer.eps, ctx, bias)
         if self.feed_forward is not None:
             x = self._join(resid, self.feed_forward.forward(x, ctx), self.norm_feed_forward.gain, self.norm_feed_forward.eps, ctx)
         if self.side_input is not None:

@@ -13,6 +13,12 @@ import math
 import torch
 
 F = torch.float64
+ROUND = None  # a dtype: activations pass through it wherever a 16-bit pipeline would store them (`forward(..., rounded=)`)
+
+
+def r(t):
+    """What a reduced-precision pipeline keeps of an activation; the identity unless `ROUND` is set."""
+    return t if ROUND is None else t.to(ROUND).to(F)
 
 
 def rms_norm(x, w, eps):
@@ -79,32 +85,32 @@ def latent_attention(h, w: dict, m: dict, eps: float):
     """h [T, width]; `w`: the mixer's tensors by their short names; `m`: the layer's "mixer" block."""
     T = h.shape[0]
     H, d, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
-    q = (h @ w["q"].T).view(T, H, d)
-    c = rms_norm(h @ w["dkv"].T, w["dkv.norm"], eps)                        # [T, rank]
-    k = (c @ w["uk"].T).view(T, H, d)
-    v = (c @ w["uv"].T).view(T, H, dv)
+    q = r(h @ w["q"].T).view(T, H, d)
+    c = r(rms_norm(r(h @ w["dkv"].T), w["dkv.norm"], eps))                  # [T, rank]
+    k = r(c @ w["uk"].T).view(T, H, d)
+    v = r(c @ w["uv"].T).view(T, H, dv)
     scores = torch.einsum("ihd,jhd->hij", q, k) * float(m["scale"])
     p = softmax_rows(scores, chunk_mask(T, None))
-    o = torch.einsum("hij,jhe->ihe", p, v).reshape(T, H * dv)
-    o = o * torch.sigmoid(h @ w["g"].T)
-    return o @ w["o"].T
+    o = r(torch.einsum("hij,jhe->ihe", p, v).reshape(T, H * dv))
+    o = r(o * torch.sigmoid(r(h @ w["g"].T)))
+    return r(o @ w["o"].T)
 
 
 def attention_keys(h, w: dict, m: dict, eps: float, positions):
     """The keys (normed over the whole projection, rotated) and values a layer forms: ([T, G, d], [T, G, dv])."""
     T = h.shape[0]
     G, d, dv = int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    k = rms_norm(h @ w["k"].T + w["k.b"], w["k.norm"], eps).view(T, G, d)
-    v = (h @ w["v"].T + w["v.b"]).view(T, G, dv)
-    return rotate_half(k, positions, m.get("rot")), v
+    k = rms_norm(r(h @ w["k"].T) + w["k.b"], w["k.norm"], eps).view(T, G, d)
+    v = r(r(h @ w["v"].T) + w["v.b"]).view(T, G, dv)
+    return r(rotate_half(k, positions, m.get("rot"))), v
 
 
 def attention(h, w: dict, m: dict, eps: float, positions, kv):
     """`kv`: (keys, values) of this layer or of the layer it borrows them from."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    q = rms_norm(h @ w["q"].T + w["q.b"], w["q.norm"], eps).view(T, H, d)
-    q = rotate_half(q, positions, m.get("rot"))
+    q = rms_norm(r(h @ w["q"].T) + w["q.b"], w["q.norm"], eps).view(T, H, d)
+    q = r(rotate_half(q, positions, m.get("rot")))
     k, v = kv
     k = k.repeat_interleave(H // G, dim=1)
     v = v.repeat_interleave(H // G, dim=1)
@@ -113,27 +119,38 @@ def attention(h, w: dict, m: dict, eps: float, positions, kv):
     if cap:
         scores = float(cap) * torch.tanh(scores / float(cap))
     p = softmax_rows(scores, chunk_mask(T, int((m.get("mask") or {}).get("size") or 0) or None))
-    o = torch.einsum("hij,jhe->ihe", p, v).reshape(T, H * dv)
-    return o @ w["o"].T + w["o.b"]
+    o = r(torch.einsum("hij,jhe->ihe", p, v).reshape(T, H * dv))
+    return r(o @ w["o"].T) + w["o.b"]
 
 
 def dense_ff(h, w: dict):
-    return (silu(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
+    return r(r(silu(r(h @ w["gate"].T)) * r(h @ w["up"].T)) @ w["down"].T)
 
 
 def token_side(x, tokens, table, i: int, dim: int, w: dict, eps: float):
     """The layer's own slice of a second embedding, gated by the stream, projected back and normed."""
     e = table[tokens][:, i * dim: (i + 1) * dim]
-    g = gelu_tanh(x @ w["gate"].T) * e
-    return rms_norm(g @ w["proj"].T, w["norm"], eps)
+    g = r(gelu_tanh(r(x @ w["gate"].T)) * e)
+    return rms_norm(r(g @ w["proj"].T), w["norm"], eps)
 
 
 def sub(weights: dict, prefix: str) -> dict:
     return {k[len(prefix):]: v.to(F) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, weights: dict, tokens, layers_out: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence.  `layers_out`, when given, receives the stream after every layer."""
+def forward(cfg: dict, weights: dict, tokens, layers_out: list | None = None, rounded=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence.  `layers_out`, when given, receives the stream after every layer.
+    `rounded`: a dtype through which the activations pass wherever a pipeline of that type would store them (the stream
+    itself, norms, scores and softmax stay exact): how far rounding alone moves the result."""
+    global ROUND
+    before, ROUND = ROUND, rounded
+    try:
+        return _forward(cfg, weights, tokens, layers_out)
+    finally:
+        ROUND = before
+
+
+def _forward(cfg: dict, weights: dict, tokens, layers_out: list | None) -> torch.Tensor:
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     T = tokens.shape[0]
     positions = torch.arange(T)
@@ -145,19 +162,19 @@ def forward(cfg: dict, weights: dict, tokens, layers_out: list | None = None) ->
         m, p = layer["mixer"], f"l{i}."
         w = sub(weights, p + "mix.")
         if layer["type"] == "latent_attention":
-            y = latent_attention(x, w, m, eps)
+            y = latent_attention(r(x), w, m, eps)
         elif layer["type"] == "attention":
             if m.get("kv_from") is None:
-                formed[i] = attention_keys(x, w, m, eps, positions)
-            y = attention(x, w, m, eps, positions, formed[i if m.get("kv_from") is None else int(m["kv_from"])])
+                formed[i] = attention_keys(r(x), w, m, eps, positions)
+            y = attention(r(x), w, m, eps, positions, formed[i if m.get("kv_from") is None else int(m["kv_from"])])
         else:
             raise ValueError(layer["type"])
         x = x + rms_norm(y, weights[p + "norm1"].to(F), eps)
         if layer.get("mlp") is not None:
-            x = x + rms_norm(dense_ff(x, sub(weights, p + "mlp.")), weights[p + "norm2"].to(F), eps)
+            x = x + rms_norm(dense_ff(r(x), sub(weights, p + "mlp.")), weights[p + "norm2"].to(F), eps)
         if side:
-            x = x + token_side(x, tokens, weights["side.embed"].to(F), i, int(side["dim"]), sub(weights, p + "side."), eps)
+            x = x + token_side(r(x), tokens, weights["side.embed"].to(F), i, int(side["dim"]), sub(weights, p + "side."), eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    x = rms_norm(x, weights["final.norm"].to(F), eps)
+    x = r(rms_norm(x, weights["final.norm"].to(F), eps))
     return x @ weights["head"].to(F).T
