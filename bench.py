@@ -27,7 +27,10 @@ layers, each beside a Llama model of equal width, feed-forward, heads and layer 
 step and one decode step of both, timed alone and set against its own bound (bytes over the copy peak, tensor flops over
 the tensor peak, CUDA-core flops over the nominal float32 rate).  `--design sorizen` does the same for Sorizen models (attention
 over a cached latent with a sink or a gate, hyper-connections, dense and routed feed-forwards) beside Dezolorn models of
-windowed attention layers alone.
+windowed attention layers alone, and `--design debuvik` for Debuvik models (latent attention with a gate on every output
+feature, chunked attention with capped scores and biases, partly on an earlier layer's keys and values, norms on the sublayers'
+outputs, the token's side input) beside Dezolorn layers of windowed attention and Sorizen layers of latent attention; `like`
+sets every Debuvik kernel's fraction of its bound over that of the sibling's kernel that does the like work.
 """
 
 from __future__ import annotations
@@ -735,6 +738,163 @@ def run_design_sorizen(args) -> dict:
     }
 
 
+# ---- Debuvik beside Dezolorn attention layers and Sorizen latent layers (--design debuvik) --------------------------------
+
+DEBUVIK_SIZES = {
+    # width, feed-forward; chunked attention: heads / kv heads / key and value head sizes / rotated features; latent attention:
+    # heads, head sizes, latent; columns of the token's side table per layer; layers (latent, attention, latent, attention
+    # on the keys and values of the attention layer two before it, and so on)
+    "w2048": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=128, vdim=64, rot=64, l_heads=16, l_dim=128, l_vdim=128, rank=512,
+                  side=64, layers=8),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, vdim=128, rot=64, l_heads=32, l_dim=128, l_vdim=128, rank=512,
+                  side=128, layers=4),
+}
+DEBUVIK_CHUNK, DEBUVIK_CAP = 1536, 30.0  # chunks that the decoding context (1,024 tokens and the timed steps) stays inside
+DEBUVIK_SIBLING_WINDOW = 1024
+
+
+def debuvik_config(sz: dict) -> dict:
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": sz["l_heads"], "dim": sz["l_dim"], "vdim": sz["l_vdim"], "kv_rank": sz["rank"], "scale": sz["l_dim"] ** -0.5}}
+
+    def attention(i: int) -> dict:
+        m = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["dim"], "vdim": sz["vdim"], "scale": sz["dim"] ** -0.5,
+             "softcap": DEBUVIK_CAP, "mask": {"size": DEBUVIK_CHUNK},
+             "rot": {"dims": sz["rot"], "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        if i % 4 == 3:
+            m["kv_from"] = i - 2
+        return {"type": "attention", "mlp": mlp, "mixer": m}
+    return {"architecture": "Debuvik", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "token_side": {"dim": sz["side"]},
+            "layers": [latent if i % 2 == 0 else attention(i) for i in range(sz["layers"])]}
+
+
+def debuvik_attention_sibling(sz: dict) -> dict:
+    """Dezolorn layers of windowed attention alone at the same width, feed-forward, heads and layer count: the closest model
+    the framework had for the chunked attention layers (the same m16n8k16 kernels, a window where Debuvik has chunks)."""
+    return windowed_sibling(dict(sz, dim=sz["dim"]))
+
+
+def debuvik_latent_sibling(sz: dict) -> dict:
+    """Sorizen layers of latent attention with a gate per head and a dense feed-forward, one plain stream, every key visible:
+    the closest model the framework had for the latent layers (the same attention kernel, plus a rotated key part)."""
+    mixer = {"heads": sz["l_heads"], "dim": sz["l_dim"], "rot_dim": 64, "vdim": sz["l_vdim"], "kv_rank": sz["rank"],
+             "scale": (sz["l_dim"] + 64) ** -0.5, "mask": {"size": 1 << 16},
+             "rot": {"dims": 64, "base": 1000000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
+    layer = {"type": "latent_attention_2", "mixer": mixer, "mlp": {"kind": "dense", "ff": sz["ff"]}}
+    return {"architecture": "Sorizen", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [layer] * sz["layers"]}
+
+
+def debuvik_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, pk: dict) -> dict[str, float]:
+    """Seconds that every kernel of one step needs at least, over all its calls (see kernel_bounds)."""
+    N = tokens or batch
+    W, L = sz["width"], sz["layers"]
+    bw, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out: dict[str, float] = {}
+    if kind == "dezolorn":
+        return sorizen_bounds("dezolorn", dict(sz, rot_dim=0, streams=1, experts=1, top=1, eff=1), tokens, batch, context, pk)
+    R, Hl, dvl = sz["rank"], sz["l_heads"], sz["l_vdim"]
+    causal = tokens * (tokens + 1) // 2 if tokens else batch * (context + 1)
+    if kind == "sorizen":
+        r = 64
+        out["ns_add_layernorm"] = 2 * L * 12.0 * N * W / bw
+        out["ns_latent_rope_store"] = L * N * 2.0 * (2 * Hl * r + 2 * (R + r)) / bw
+        out["ns_attention_latent_tc"] = L * (2.0 * Hl * (2 * R + r) * causal / tc if tokens else 2.0 * causal * (R + r) / bw)
+        out["ns_activation"] = L * 4.0 * N * sz["ff"] / bw
+        return out
+    n_lat, n_att, n_own = (L + 1) // 2, L // 2, sum(1 for i in range(L) if i % 4 == 1)
+    nq, nkv, d, dv = sz["heads"], sz["kv_heads"], sz["dim"], sz["vdim"]
+    seen = lambda p: p % DEBUVIK_CHUNK + 1  # keys of its own chunk that position p sees
+    pairs = sum(seen(p) for p in range(tokens)) if tokens else batch * seen(context)
+    # the stream read and written in float32, the branch read and the stream's copy written in bfloat16: after the mixer, the
+    # feed-forward and the side input of every layer
+    out["ns_norm_add"] = 3 * L * 12.0 * N * W / bw
+    # q read and written, k and v read and stored (layers with projections of their own)
+    out["ns_qk_norm_rope_store"] = (n_att * 4.0 * N * nq * d + n_own * 4.0 * N * nkv * (d + dv)) / bw
+    if tokens:
+        out["ns_attention_prefill_kept"] = n_att * 2.0 * nq * (d + dv) * pairs / tc
+    else:
+        out["ns_attention_decode_kept"] = n_att * 2.0 * pairs * nkv * (d + dv) / bw
+    out["ns_latent_rope_store"] = n_lat * N * 4.0 * R / bw
+    out["ns_attention_latent_tc"] = n_lat * (4.0 * Hl * R * causal / tc if tokens else 2.0 * causal * R / bw)
+    out["ns_sigmoid_mul"] = n_lat * 6.0 * N * Hl * dvl / bw
+    out["ns_swiglu"] = L * 6.0 * N * sz["ff"] / bw
+    out["ns_token_gate"] = L * 6.0 * N * sz["side"] / bw
+    return out
+
+
+# a Debuvik kernel and the kernel of a sibling that does the like work
+DEBUVIK_LIKE = {"ns_norm_add": ("dezolorn", "ns_add_layernorm"), "ns_qk_norm_rope_store": ("dezolorn", "ns_qk_norm_rope_store"),
+                "ns_attention_prefill_kept": ("dezolorn", "ns_attention_prefill_kept"),
+                "ns_attention_decode_kept": ("dezolorn", "ns_attention_decode_kept"), "ns_swiglu": ("dezolorn", "ns_swiglu"),
+                "ns_latent_rope_store": ("sorizen", "ns_latent_rope_store"), "ns_attention_latent_tc": ("sorizen", "ns_attention_latent_tc"),
+                "ns_sigmoid_mul": ("sorizen", "ns_activation"), "ns_token_gate": ("sorizen", "ns_activation")}
+
+
+def run_design_debuvik(args) -> dict:
+    import torch
+
+    from nanospec_b200 import random_model
+
+    pk, pk_src = peaks()
+    makers = {"debuvik": debuvik_config, "dezolorn": debuvik_attention_sibling, "sorizen": debuvik_latent_sibling}
+    out_sizes = {}
+    for name, sz in DEBUVIK_SIZES.items():
+        row = {}
+        for kind, maker in makers.items():
+            model = random_model(maker(sz), seed=1, device="cuda", dtype=torch.bfloat16)
+            pages_per_req = -(-(CONTEXT + args.repeats * args.steps + args.warmup + 64) // PAGE)
+            eng = design_engine(model, 64, max(64 * pages_per_req, -(-PREFILL_TOKENS // PAGE) + 8) + 8)
+            rec = {}
+            for b in (8, 64):
+                pt = time_decode(eng, b, args.steps, args.warmup, args.repeats)
+                rec[f"decode_b{b}_tok_s"] = round(b * 1000.0 / pt["ms"], 1)
+                rec[f"decode_b{b}_ms"] = round(pt["ms"], 4)
+                rec[f"decode_b{b}_clocks"] = {"sm_mhz": pt["clocks"].get("sm_mhz"), "reasons": pt["clocks"].get("reasons")}
+                if b == 8 and kind == "debuvik" and name == "w4096":
+                    headline = pt
+            pre_ms, pre_clocks = time_prefill(eng, warmup=3, iters=5)
+            rec["prefill_tok_s"] = round(PREFILL_TOKENS * 1000.0 / pre_ms, 1)
+            rec["prefill_ms"] = round(pre_ms, 3)
+            rec["prefill_clocks"] = {"sm_mhz": pre_clocks.get("sm_mhz"), "reasons": pre_clocks.get("reasons")}
+            del eng
+            torch.cuda.empty_cache()
+            kernels = {}
+            for what, tokens, batch in (("prefill", PREFILL_TOKENS, 0), ("decode_b64", 0, 64)):
+                timed = time_kernels(model, tokens, batch, CONTEXT)
+                bounds = debuvik_bounds(kind, sz, tokens, batch, CONTEXT, pk)
+                kernels[what] = {k: {"calls": n, "ms": round(ms, 4), "bound_ms": round(bounds[k] * 1e3, 4) if k in bounds else None,
+                                     "frac": round(bounds[k] * 1e3 / ms, 4) if k in bounds and ms > 0 else None}
+                                 for k, (n, ms) in sorted(timed.items(), key=lambda kv: -kv[1][1])}
+            rec["kernels"] = kernels
+            row[kind] = rec
+            del model
+            torch.cuda.empty_cache()
+        # every Debuvik kernel's fraction of its bound over the like kernel's of a sibling (below 0.5: more than twice as far)
+        like = {}
+        for what in ("prefill", "decode_b64"):
+            for k, v in row["debuvik"]["kernels"][what].items():
+                other = row[DEBUVIK_LIKE[k][0]]["kernels"][what].get(DEBUVIK_LIKE[k][1]) if k in DEBUVIK_LIKE else None
+                if v["frac"] and other and other["frac"]:
+                    like[f"{what}:{k}"] = {"frac": v["frac"], "like": "/".join(DEBUVIK_LIKE[k]), "like_frac": other["frac"],
+                                           "ratio": round(v["frac"] / other["frac"], 3)}
+        row["like"] = like
+        out_sizes[name] = row
+    value = out_sizes["w4096"]["debuvik"]["decode_b8_tok_s"]
+    return {
+        "metric": "decode tok/s (Debuvik, width 4,096, 4 layers, batch 8, 1,024-token context)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": out_sizes["w4096"]["debuvik"]["decode_b8_ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform random token ids, random weights",
+        "config": {"design": "debuvik beside dezolorn (attention layers) and sorizen (latent layers)", "sizes": DEBUVIK_SIZES,
+                   "vocab": DESIGN_VOCAB, "chunk": DEBUVIK_CHUNK, "softcap": DEBUVIK_CAP, "sibling_window": DEBUVIK_SIBLING_WINDOW,
+                   "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "page": PAGE, "cuda_graphs": True, "peaks": pk_src,
+                   "l2": "the weights of every step are larger than L2"},
+        "gpu_launches": headline["launches"], "clocks": headline["clocks"], "sizes": out_sizes,
+    }
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
 
@@ -751,7 +911,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"])
     ap.add_argument("--no-workloads", action="store_true", help="leave out the 3B continuous-batching and 1B mixed workloads")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--design", choices=["dezolorn", "sorizen"], help="measure this design beside its closest sibling of equal size instead")
+    ap.add_argument("--design", choices=["dezolorn", "sorizen", "debuvik"], help="measure this design beside its closest sibling of equal size instead")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.repeats = max(1, args.repeats)
@@ -759,7 +919,7 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
-    out = run_reference(args) if args.impl == "reference" else run_design_sorizen(args) if args.design == "sorizen" else run_design(args) if args.design else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else run_design_sorizen(args) if args.design == "sorizen" else run_design_debuvik(args) if args.design == "debuvik" else run_design(args) if args.design else run_ours(args)
     print(json.dumps(out), flush=True)
     return 0
 

@@ -108,7 +108,7 @@ class DebuvikConfig:
                 ff = int(_need(mlp, "ff", where + ".mlp"))
             layers.append(DebuvikLayer(kind, m, ff))
         side = cfg.get("token_side")
-        side_dim = int(_need(side, "dim", "token_side")) if side else 0
+        side_dim = int(_need(side, "dim", "token_side")) if side is not None else 0
         eos = (generation or {}).get("eos_token_id", cfg.get("eos_token_id"))
         eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
         return cls(vocab=int(_need(cfg, "vocab", "config.json")), width=int(_need(cfg, "width", "config.json")),

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(128)
 latent_rope_store_kernel(T* __restrict__ proj, int proj_stride, const int* __restrict__ positions,
                          const int* __restrict__ token_req, const int* __restrict__ block_table, int table_stride,
                          const float* __restrict__ inv_freq, float magnitude, int n_pairs, const float* __restrict__ gain,
-                         float eps, T* __restrict__ cache, int page_size, int H, int d, int r, int R, int write) {
+                         float eps, T* __restrict__ cache, int page_size, int H, int d, int r, int R, int write, int vec) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
     __shared__ float scratch[32];
@@ -40,7 +40,24 @@ latent_rope_store_kernel(T* __restrict__ proj, int proj_stride, const int* __res
         dst = cache + ((size_t)page * page_size + pos % page_size) * (size_t)(R + r);
     }
     // the latent's norm: two passes, float
-    if (write) {
+    if (write && vec) {  // 8 features per access: every size and offset a multiple of 8, pointers on 16 bytes
+        float ss = 0.f;
+        for (int e = tid * 8; e < R; e += blockDim.x * 8) {
+            float v[8];
+            ld8(lat + e, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += v[k] * v[k];
+        }
+        const float inv = 1.f / sqrtf(ns_block_sum(ss, scratch) / (float)R + eps);
+        for (int e = tid * 8; e < R; e += blockDim.x * 8) {
+            float v[8], g[8];
+            ld8(lat + e, v);
+            ld8(gain + e, g);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = v[k] * inv * g[k];
+            st8(dst + e, v);
+        }
+    } else if (write) {
         float ss = 0.f;
         for (int e = tid; e < R; e += blockDim.x) {
             const float v = ns_ld(lat, e);
@@ -212,13 +229,18 @@ NS_API int ns_latent_rope_store(void* proj, int proj_stride, const int* position
     if (n_tokens <= 0) return NS_OK;
     if (2 * n_pairs > r || n_pairs < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_latent_rope_store: %d pairs do not fit %d rotated features", n_pairs, r);
     if (write && (!cache || !block_table || !gain)) NS_FAIL(NS_ERR_ARGUMENT, "ns_latent_rope_store: a write needs the cache, the table and the gain");
+    // (which form of the norm runs depends on sizes and alignment only, never on the batch)
+    const size_t elem = dtype == NS_F32 ? 4 : 2;
+    const int vec = R % 8 == 0 && r % 8 == 0 && (H * (d + r)) % 8 == 0 && proj_stride % 8 == 0 &&
+                    ((uintptr_t)proj % (8 * elem) == 0) && ((uintptr_t)cache % (8 * elem) == 0) && ((uintptr_t)gain % 16 == 0);
+    const int threads = R <= 512 && vec ? 64 : 128;
     if (dtype == NS_F32)
-        NS_LAUNCH((latent_rope_store_kernel<float>), n_tokens, 128, 0, stream, (float*)proj, proj_stride, positions, token_req,
-                  block_table, table_stride, inv_freq, magnitude, n_pairs, gain, eps, (float*)cache, page_size, H, d, r, R, write);
+        NS_LAUNCH((latent_rope_store_kernel<float>), n_tokens, threads, 0, stream, (float*)proj, proj_stride, positions, token_req,
+                  block_table, table_stride, inv_freq, magnitude, n_pairs, gain, eps, (float*)cache, page_size, H, d, r, R, write, vec);
     else if (dtype == NS_BF16)
-        NS_LAUNCH((latent_rope_store_kernel<__nv_bfloat16>), n_tokens, 128, 0, stream, (__nv_bfloat16*)proj, proj_stride, positions,
+        NS_LAUNCH((latent_rope_store_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, (__nv_bfloat16*)proj, proj_stride, positions,
                   token_req, block_table, table_stride, inv_freq, magnitude, n_pairs, gain, eps, (__nv_bfloat16*)cache, page_size, H,
-                  d, r, R, write);
+                  d, r, R, write, vec);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_latent_rope_store: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_latent_rope_store");

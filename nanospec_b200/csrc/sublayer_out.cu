@@ -151,6 +151,74 @@ __global__ void sigmoid_mul_kernel(T* __restrict__ x, long long ldx, const T* __
     ns_st(x, n * ldx + c, ns_ld(x, n * ldx + c) * (1.f / (1.f + expf(-z))));
 }
 
+// The same two with 8 consecutive features per thread (16-byte accesses in bfloat16): widths, leading sizes and offsets in
+// multiples of 8 and pointers on 16 bytes.  Which form runs depends on sizes and alignment only, never on the batch.
+template <typename T>
+__global__ void token_gate_vec_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ table, long long ldt,
+                                      const int* __restrict__ ids, int vocab, int off, T* __restrict__ out, int groups, size_t total) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / groups;
+    const int j = (int)(i - n * groups) * 8;
+    const int id = ids[n];
+    float e[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, z[8];
+    if (id >= 0 && id < vocab) ld8(table + (size_t)id * ldt + off + j, e);
+    ld8(a + n * lda + j, z);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) z[k] = gelu_tanh_f(z[k]) * e[k];
+    st8(out + i * 8, z);
+}
+
+template <typename T>
+__global__ void sigmoid_mul_vec_kernel(T* __restrict__ x, long long ldx, const T* __restrict__ g, long long ldg, int groups, size_t total) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / groups;
+    const int c = (int)(i - n * groups) * 8;
+    float z[8], v[8];
+    ld8(g + n * ldg + c, z);
+    ld8(x + n * ldx + c, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= 1.f / (1.f + expf(-z[k]));
+    st8(x + n * ldx + c, v);
+}
+
+template <typename T>
+int launch_token_gate(const void* a, long long lda, const void* table, long long ldt, const int* ids, int vocab, int off, void* out,
+                      int n_rows, int dim, cudaStream_t stream) {
+    const bool vec = dim % 8 == 0 && lda % 8 == 0 && ldt % 8 == 0 && off % 8 == 0 &&
+                     (((uintptr_t)a | (uintptr_t)table | (uintptr_t)out) % (8 * sizeof(T)) == 0);
+    if (vec) {
+        const size_t total = (size_t)n_rows * (dim / 8);
+        NS_LAUNCH((token_gate_vec_kernel<T>), (unsigned)((total + 127) / 128), 128, 0, stream, (const T*)a, lda, (const T*)table, ldt, ids,
+                  vocab, off, (T*)out, dim / 8, total);
+    } else {
+        const size_t total = (size_t)n_rows * dim;
+        NS_LAUNCH((token_gate_kernel<T>), (unsigned)((total + 255) / 256), 256, 0, stream, (const T*)a, lda, (const T*)table, ldt, ids,
+                  vocab, off, (T*)out, dim, total);
+    }
+    NS_CHECK_LAUNCH("ns_token_gate");
+    return NS_OK;
+}
+
+template <typename T>
+int launch_sigmoid_mul(void* x, long long ldx, const void* g, long long ldg, int n_rows, int cols, cudaStream_t stream) {
+    const bool vec = cols % 8 == 0 && ldx % 8 == 0 && ldg % 8 == 0 && (((uintptr_t)x | (uintptr_t)g) % (8 * sizeof(T)) == 0);
+    if (vec) {
+        const size_t total = (size_t)n_rows * (cols / 8);
+        NS_LAUNCH((sigmoid_mul_vec_kernel<T>), (unsigned)((total + 127) / 128), 128, 0, stream, (T*)x, ldx, (const T*)g, ldg, cols / 8, total);
+    } else {
+        const size_t total = (size_t)n_rows * cols;
+        NS_LAUNCH((sigmoid_mul_kernel<T>), (unsigned)((total + 255) / 256), 256, 0, stream, (T*)x, ldx, (const T*)g, ldg, cols, total);
+    }
+    NS_CHECK_LAUNCH("ns_sigmoid_mul");
+    return NS_OK;
+}
+
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, long long ldx, const float* __restrict__ bias, int cols, size_t total) {
     ns_pdl_launch_dependents();
@@ -178,33 +246,17 @@ NS_API int ns_norm_add(float* resid, const void* branch, const float* bias, cons
 
 NS_API int ns_token_gate(const void* a, long long lda, const void* table, long long ldt, const int* ids, int vocab, int off,
                          void* out, int n_rows, int dim, int dtype, cudaStream_t stream) {
-    const size_t total = (size_t)n_rows * dim;
-    if (total == 0) return NS_OK;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == NS_F32)
-        NS_LAUNCH((token_gate_kernel<float>), blocks, 256, 0, stream, (const float*)a, lda, (const float*)table, ldt, ids, vocab, off,
-                  (float*)out, dim, total);
-    else if (dtype == NS_BF16)
-        NS_LAUNCH((token_gate_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)table,
-                  ldt, ids, vocab, off, (__nv_bfloat16*)out, dim, total);
-    else
-        NS_FAIL(NS_ERR_ARGUMENT, "ns_token_gate: unknown dtype %d", dtype);
-    NS_CHECK_LAUNCH("ns_token_gate");
-    return NS_OK;
+    if ((size_t)n_rows * dim == 0) return NS_OK;
+    if (dtype == NS_F32) return launch_token_gate<float>(a, lda, table, ldt, ids, vocab, off, out, n_rows, dim, stream);
+    if (dtype == NS_BF16) return launch_token_gate<__nv_bfloat16>(a, lda, table, ldt, ids, vocab, off, out, n_rows, dim, stream);
+    NS_FAIL(NS_ERR_ARGUMENT, "ns_token_gate: unknown dtype %d", dtype);
 }
 
 NS_API int ns_sigmoid_mul(void* x, long long ldx, const void* g, long long ldg, int n_rows, int cols, int dtype, cudaStream_t stream) {
-    const size_t total = (size_t)n_rows * cols;
-    if (total == 0) return NS_OK;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == NS_F32)
-        NS_LAUNCH((sigmoid_mul_kernel<float>), blocks, 256, 0, stream, (float*)x, ldx, (const float*)g, ldg, cols, total);
-    else if (dtype == NS_BF16)
-        NS_LAUNCH((sigmoid_mul_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)g, ldg, cols, total);
-    else
-        NS_FAIL(NS_ERR_ARGUMENT, "ns_sigmoid_mul: unknown dtype %d", dtype);
-    NS_CHECK_LAUNCH("ns_sigmoid_mul");
-    return NS_OK;
+    if ((size_t)n_rows * cols == 0) return NS_OK;
+    if (dtype == NS_F32) return launch_sigmoid_mul<float>(x, ldx, g, ldg, n_rows, cols, stream);
+    if (dtype == NS_BF16) return launch_sigmoid_mul<__nv_bfloat16>(x, ldx, g, ldg, n_rows, cols, stream);
+    NS_FAIL(NS_ERR_ARGUMENT, "ns_sigmoid_mul: unknown dtype %d", dtype);
 }
 
 NS_API int ns_add_bias(void* x, long long ldx, const float* bias, int n_rows, int cols, int dtype, cudaStream_t stream) {

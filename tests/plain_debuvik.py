@@ -13,12 +13,14 @@ import math
 import torch
 
 F = torch.float64
-ROUND = None  # a dtype: activations pass through it wherever a 16-bit pipeline would store them (`forward(..., rounded=)`)
+ROUND = None  # a dtype, or a function of a tensor: activations pass through it wherever a 16-bit pipeline would store them (`forward(..., rounded=)`)
 
 
 def r(t):
     """What a reduced-precision pipeline keeps of an activation; the identity unless `ROUND` is set."""
-    return t if ROUND is None else t.to(ROUND).to(F)
+    if ROUND is None:
+        return t
+    return ROUND(t) if callable(ROUND) else t.to(ROUND).to(F)
 
 
 def rms_norm(x, w, eps):
@@ -141,7 +143,8 @@ def sub(weights: dict, prefix: str) -> dict:
 def forward(cfg: dict, weights: dict, tokens, layers_out: list | None = None, rounded=None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  `layers_out`, when given, receives the stream after every layer.
     `rounded`: a dtype through which the activations pass wherever a pipeline of that type would store them (the stream
-    itself, norms, scores and softmax stay exact): how far rounding alone moves the result."""
+    itself, norms, scores and softmax stay exact), or a function that stands for such a storage: how far rounding alone moves
+    the result."""
     global ROUND
     before, ROUND = ROUND, rounded
     try:
