@@ -136,7 +136,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int key = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
-                    const float v = key >= k1 ? -INFINITY : softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
+                    const float v = key >= k1 ? -INFINITY : softcap > 0.f ? cap_out * ns_tanh_fast(s[nb][j] * cap_in) : s[nb][j] * sl;
                     s[nb][j] = v;
                     mx[j >> 1] = fmaxf(mx[j >> 1], v);
                 }

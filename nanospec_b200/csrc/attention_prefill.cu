@@ -136,7 +136,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float v = softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
+                        const float v = softcap > 0.f ? cap_out * ns_tanh_fast(s[nb][j] * cap_in) : s[nb][j] * sl;
                         s[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }
@@ -150,7 +150,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                         const int p = prow[j >> 1];
                         const bool seen = key <= p && (window <= 0 || key > p - window || key < keep_first) && vkey >= kfirst &&
                                           key >= cfirst[j >> 1];
-                        const float v = !seen ? -INFINITY : softcap > 0.f ? cap_out * tanhf(s[nb][j] * cap_in) : s[nb][j] * sl;
+                        const float v = !seen ? -INFINITY : softcap > 0.f ? cap_out * ns_tanh_fast(s[nb][j] * cap_in) : s[nb][j] * sl;
                         s[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }

@@ -51,6 +51,14 @@ __device__ __forceinline__ float ns_exp2(float x) {
     return y;
 }
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) with the one-instruction exponential and reciprocal: absolute error about 2e-7 everywhere
+// (x is clamped to +-15, beyond which the float result is +-1).  A capped score c * tanh(s / c) carries it as c * 2e-7, far
+// below what bfloat16 operands leave in s itself; the exact kernel keeps tanhf.
+__device__ __forceinline__ float ns_tanh_fast(float x) {
+    const float e = ns_exp2(fminf(fmaxf(x, -15.f), 15.f) * 2.8853900817779268f);
+    return 1.f - __fdividef(2.f, e + 1.f);
+}
+
 __device__ __forceinline__ uint32_t ns_pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
