@@ -510,11 +510,12 @@ def test_configurations_drawn_from_seeds(seed, tmp_path):
         mlp = pick([None, dense(pick([8, 20, 64]))])
         kind = pick(["latent", "attention", "attention"])
         if kind == "latent":
-            layers.append(latent(mlp, heads=pick([1, 2, 3, 7]), dim=pick([2, 8, 12, 32]), vdim=pick([2, 8, 20]), rank=pick([4, 16, 36, 64])))
+            layers.append(latent(mlp, heads=pick([1, 2, 3, 7]), dim=pick([2, 8, 12, 32]), vdim=pick([2, 8, 20]), rank=pick([4, 16, 36, 64]),
+                                 scale=pick([None, 0.3, 0.05])))
             continue
         dim = pick([2, 8, 12, 32])
         kw = dict(size=pick([0, 1, 3, 8, 33]), dims=pick([None, 0, 2, dim]), base=pick([100.0, 50000.0]), scaling=pick([None, BANDS]),
-                  softcap=pick([0, 1.0, 20.0]))
+                  softcap=pick([0, 1.0, 20.0]), scale=pick([None, 0.6, 0.11]))
         if lenders and pick([True, False]):
             src = pick(lenders)
             sm = layers[src]["mixer"]
@@ -525,7 +526,7 @@ def test_configurations_drawn_from_seeds(seed, tmp_path):
             kv = pick([1, 2, 3])
             layers.append(attention(mlp, heads=kv * pick([1, 2, 4]), kv_heads=kv, dim=dim, vdim=pick([2, 8, 20, dim]), **kw))
             lenders.append(i)
-    cfg = config(layers, width=pick([16, 24, 72]), vocab=pick([50, 131]), side=pick([0, 1, 4]))
+    cfg = config(layers, width=pick([16, 24, 72]), vocab=pick([50, 131]), side=pick([0, 1, 4]), eps=pick([1e-5, 1e-6, 1e-3]))
     for dtype in (F32, BF16):
         runner, w = make(tmp_path, cfg, seed=seed, dtype=dtype, page=pick([2, 4, 16]))
         ids = tokens(48, cfg["vocab"], seed)
