@@ -58,7 +58,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int kend = pos + 1;
     // With kept first keys behind a window the block counts keys in a virtual range [kstart, kend) in which the kept keys
     // lie directly before the window: a virtual key below win_start is the real key (virtual - gap); see load_kv_tile.
-    // mask_chunk > 0: the query sees only the keys of its own chunk of that many positions, counted from position 0.
+    // mask_chunk > 0: the query sees only the keys of its own chunk of that many positions, counted from the start of the sequence.
     int win_start = (window > 0 && kend - window > 0) ? kend - window : 0;
     if (mask_chunk > 0) win_start = max(win_start, (pos / mask_chunk) * mask_chunk);
     const int gap = win_start - min(keep_first, win_start);

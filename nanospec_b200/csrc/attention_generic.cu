@@ -9,7 +9,7 @@
 // A query at position p of request r sees the keys at positions max(0, p - window + 1) .. p
 // of the same request (window == 0: all of 0 .. p) and, with keep_first > 0, also the keys at
 // positions 0 .. keep_first - 1 however far back they lie (they keep their own positions).  With chunk > 0 the
-// sequence is cut into chunks of that many positions counted from position 0 and a query sees only the keys of its
+// sequence is cut into chunks of that many positions counted from the start of the sequence and a query sees only the keys of its
 // own chunk: the first visible key is then no earlier than floor(p / chunk) * chunk.  With softcap > 0 a score s
 // (after the scale) becomes softcap * tanh(s / softcap) before the softmax.  Keys and
 // values are read from cache[page, kv_head, offset, :] with page = block_table[r, position / page_size];

@@ -10,7 +10,7 @@
 // max(0, p - window + 1) .. p (window 0: all of 0 .. p) and, with keep_first > 0, the keys 0 .. keep_first - 1 as
 // well: the block then counts keys in a virtual range in which the kept keys lie directly before the first row's
 // window (see load_kv_tile) and masks by the real key.  With mask_chunk > 0 a query sees only the keys of its own
-// chunk of that many positions (chunks counted from position 0): the first visible key is no earlier than
+// chunk of that many positions (chunks counted from the start of the sequence): the first visible key is no earlier than
 // floor(p / mask_chunk) * mask_chunk.  With softcap > 0 a scaled score s becomes softcap * tanh(s / softcap).
 // Keys of dk and values of dv features (multiples of 8) run in the instance for D = the larger of the two rounded up to 16:
 // the tiles' columns beyond dk and dv are zero, and the products skip the 16-column steps that lie wholly beyond them.

@@ -659,7 +659,7 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     that bring one token, the prefill kernel for the others.  `wide_weights`: the softmax weights meet the values
     with about 16 bits each (two bfloat16 products per weight) instead of 8, for designs that state their weights in
     float32; the m16n8k16 kernels have it.  `chunk` > 0: a query sees only the keys of its own chunk of that many
-    positions, counted from position 0; `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the exact and
+    positions, counted from the start of the sequence; `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the exact and
     the m16n8k16 kernels); `v_dim`: values of another width than the keys (the same kernels, widths in multiples of 8).  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim

@@ -33,7 +33,7 @@ class GQAAttention(Part):
     qk_norm      {"eps": e}: an RMS norm over the whole q projection and one over the whole k projection (one statistic
                  over all heads, gains `q_norm` / `k_norm` of the projections' sizes), before the rotation
     wide_weights True: the softmax weights keep about 16 bits where they meet the values (`ops.attention`)
-    chunk        c > 0: the sequence is cut into chunks of c positions counted from position 0 and a query sees only the
+    chunk        c > 0: the sequence is cut into chunks of c positions counted from the start of the sequence and a query sees only the
                  keys of its own chunk (at or before its position)
     softcap      c > 0: a scaled score s becomes c * tanh(s / c) before the softmax
     bias         True: q, k, v and o have biases (float32 in every mode; names "q_bias", "k_bias", "v_bias", "o_bias",

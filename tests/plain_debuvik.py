@@ -70,7 +70,7 @@ def rotate_half(x, positions, rot: dict | None):
 
 
 def chunk_mask(T: int, size: int | None) -> torch.Tensor:
-    """mask[i, j]: j <= i and, with a chunk size, both in the same chunk counted from position 0."""
+    """mask[i, j]: j <= i and, with a chunk size, both in the same chunk counted from the start of the sequence."""
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
     ok = j <= i
