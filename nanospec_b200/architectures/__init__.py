@@ -1,3 +1,3 @@
-from . import debuvik, dezolorn, llama, sorizen  # registers Debuvik, Dezolorn, LlamaForCausalLM and Sorizen
+from . import debuvik, dezolorn, fubolix, llama, sorizen  # registers Debuvik, Dezolorn, Fubolix, LlamaForCausalLM and Sorizen
 
-__all__ = ["debuvik", "dezolorn", "llama", "sorizen"]
+__all__ = ["debuvik", "dezolorn", "fubolix", "llama", "sorizen"]

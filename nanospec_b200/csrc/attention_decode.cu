@@ -35,7 +35,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
                         int n_splits, int head_tiles, int keep_first, int wide_weights, int mask_chunk, float softcap,
-                        int dk, int dv) {
+                        int dk, int dv, const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -233,7 +233,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         }
         const int h = h0 + row;
         if (n_splits == 1) {
-            out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(acc / lt);
+            // a sink: exp(sink[h]) joins the denominator (maxima and sums are in base 2); a gate: the head's output times its sigmoid
+            if (sink) lt += ns_exp2(sink[h] * kLog2e - mt);
+            float res = acc / lt;
+            if (gate) res *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)n * gate_stride + h])));
+            out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(res);
         } else {
             const size_t slot = ((size_t)z * nq + h) * n_splits + split;
             part_o[slot * D + col] = acc;
@@ -281,7 +285,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             acc += os[s2] * f;
             lt += ls[s2] * f;
         }
-        out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(acc / lt);
+        if (sink) lt += ns_exp2(sink[h] * kLog2e - mt);
+        float res = acc / lt;
+        if (gate) res *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)n * gate_stride + h])));
+        out[(size_t)n * o_stride + (size_t)h * dv + col] = __float2bfloat16_rn(res);
     }
 }
 
@@ -290,7 +297,7 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
                   int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first, int wide_weights,
-                  int mask_chunk, float softcap, int dk, int dv) {
+                  int mask_chunk, float softcap, int dk, int dv, const float* sink, const void* gate, int gate_stride) {
     constexpr int S = NsTile<D>::kStride;
     const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
@@ -305,7 +312,8 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
     NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
-        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
+        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights, mask_chunk, softcap, dk, dv, sink,
+        (const __nv_bfloat16*)gate, gate_stride);
     NS_CHECK_LAUNCH("ns_attention_decode");
     return NS_OK;
 }
@@ -317,14 +325,14 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
                   int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first, int wide_weights,
-                  int mask_chunk, float softcap, int dk, int dv) {
+                  int mask_chunk, float softcap, int dk, int dv, const float* sink, const void* gate, int gate_stride) {
     if (g_decode_stages == 2)
         return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                           qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
+                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv, sink, gate, gate_stride);
     return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                       qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
+                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv, sink, gate, gate_stride);
 }
 
 }  // namespace
@@ -355,12 +363,14 @@ NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int
 // becomes softcap * tanh(s / softcap).  Kept first keys and chunks do not go together.
 // `dv` > 0: values of that many features where the keys have `d` (both multiples of 8 then; the output rows are nq * dv wide
 // and `part_o` holds as many columns per row as the instance that runs: the larger of d and dv rounded up to 16).
+// `sink` (optional, float [nq]): every query's denominator also holds exp(sink[h]), a term without key or value, counted once
+// however the keys are split.  `gate` (optional, bfloat16, gate[token * gate_stride + h]): head h's output times the sigmoid of its gate.
 NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_stride, const int* token_req, const int* positions,
                                     const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
                                     int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
                                     float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap, int n_splits,
-                                    int dv, cudaStream_t stream) {
+                                    int dv, const float* sink, const void* gate, int gate_stride, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
@@ -378,7 +388,7 @@ NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_c
     case DD:                                                                                                           \
         return launch_decode<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,       \
                                  qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,         \
-                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv);
+                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights, mask_chunk, softcap, dk, dv, sink, gate, gate_stride);
     switch (dmax) {
         NS_DECODE_CASE(16) NS_DECODE_CASE(32) NS_DECODE_CASE(48) NS_DECODE_CASE(64)
         NS_DECODE_CASE(80) NS_DECODE_CASE(96) NS_DECODE_CASE(112) NS_DECODE_CASE(128)
@@ -394,7 +404,7 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
                                float scale, int window, int n_splits, cudaStream_t stream) {
     return ns_attention_decode_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr, out,
                                     o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0, 0,
-                                    0, 0.f, n_splits, 0, stream);
+                                    0, 0.f, n_splits, 0, nullptr, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -27,7 +27,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_req, const int* __restrict__ positions, T* __restrict__ out,
                          int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
-                         int keep_first, int chunk, float softcap) {
+                         int keep_first, int chunk, float softcap, const float* __restrict__ sink,
+                         const T* __restrict__ gate, int gate_stride) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     extern __shared__ float qsm[];
@@ -94,7 +95,15 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         m = m_new;
     }
     }
-    const float inv = 1.f / l;
+    if (sink) {  // a term of the denominator that has no key and no value: exp(sink[h])
+        const float m_new = fmaxf(m, sink[h]);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sink[h] - m_new);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+    }
+    float inv = 1.f / l;
+    if (gate) inv *= 1.f / (1.f + expf(-ns_ld(gate, (size_t)n * gate_stride + h)));  // the head's output gate
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
         const int e = lane + 32 * i;
@@ -105,7 +114,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
 template <typename T>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int table_stride, const int* token_req, const int* positions, void* out, int o_stride, int n_tokens, int nq,
-           int nkv, int d, int dv, int page_size, float scale, int window, int keep_first, int chunk, float softcap, cudaStream_t stream) {
+           int nkv, int d, int dv, int page_size, float scale, int window, int keep_first, int chunk, float softcap,
+           const float* sink, const void* gate, int gate_stride, cudaStream_t stream) {
     const long long warps = (long long)n_tokens * nq;
     const unsigned blocks = (unsigned)((warps + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
@@ -114,7 +124,8 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     case D:                                                                                                          \
         NS_LAUNCH((attention_generic_kernel<T, D>), blocks, kWarpsPerBlock * 32, smem, stream,                                \
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride, token_req,       \
-            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap);                           \
+            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, \
+            sink, (const T*)gate, gate_stride);                                                                       \
         break;
     switch (dpl) {
         NS_ATTN_CASE(1) NS_ATTN_CASE(2) NS_ATTN_CASE(3) NS_ATTN_CASE(4)
@@ -127,10 +138,14 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 
 }  // namespace
 
-NS_API int ns_attention_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+// `sink` (optional, float [nq]): every query's denominator also holds exp(sink[h]), a term without key or value (zeros: "one
+// added to the denominator").  `gate` (optional, the activations' type, one number per token and head at
+// gate[n * gate_stride + h]): head h's output is multiplied by its sigmoid.
+NS_API int ns_attention_generic_sink(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* token_req, const int* positions,
                                 void* out, int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size,
-                                float scale, int window, int keep_first, int chunk, float softcap, int dtype, cudaStream_t stream) {
+                                float scale, int window, int keep_first, int chunk, float softcap, const float* sink,
+                                const void* gate, int gate_stride, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (d < 1 || d > 256 || dv < 1 || dv > 256)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: head sizes %d (keys) and %d (values) must lie in 1..256", d, dv);
@@ -139,9 +154,18 @@ NS_API int ns_attention_generic(const void* q, int q_stride, const void* k_cache
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: %d query heads over %d kv heads", nq, nkv);
     if (dtype == NS_F32)
         return launch<float>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, out,
-                             o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, stream);
+                             o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, sink, gate, gate_stride, stream);
     if (dtype == NS_BF16)
         return launch<__nv_bfloat16>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
-                                     out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, stream);
+                                     out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, sink, gate, gate_stride, stream);
     NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: unknown dtype %d", dtype);
+}
+
+NS_API int ns_attention_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                const int* block_table, int table_stride, const int* token_req, const int* positions,
+                                void* out, int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size,
+                                float scale, int window, int keep_first, int chunk, float softcap, int dtype, cudaStream_t stream) {
+    return ns_attention_generic_sink(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, out, o_stride,
+                                     n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, chunk, softcap, nullptr, nullptr,
+                                     0, dtype, stream);
 }

@@ -31,7 +31,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
                          int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap,
-                         int dk, int dv) {
+                         int dk, int dv, const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -219,7 +219,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     for (int i = 0; i < 2; ++i) {
         const int row = warp * 16 + (lane >> 2) + 8 * i;
         if (row >= rows) continue;
-        const float inv = 1.f / l[i];
+        // a sink: exp(sink[h]) joins the denominator (m and the sums are in base 2); a gate: the head's output times its sigmoid
+        if (sink) l[i] += ns_exp2(sink[h] * kLog2e - m[i]);
+        float inv = 1.f / l[i];
+        if (gate) inv *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)(tok0 + row) * gate_stride + h])));
         __nv_bfloat16* orow = out + (size_t)(tok0 + row) * o_stride + (size_t)h * dv;
 #pragma unroll
         for (int nb = 0; nb < D / 8; ++nb) {
@@ -233,7 +236,8 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                    int table_stride, const int* positions, const int* qo_indptr, const int* tiles, int n_tiles,
                    void* out, int o_stride, int nq, int nkv, int page_size, float scale, int window,
-                   cudaStream_t stream, int keep_first, int wide_weights, int mask_chunk, float softcap, int dk, int dv) {
+                   cudaStream_t stream, int keep_first, int wide_weights, int mask_chunk, float softcap, int dk, int dv,
+                   const float* sink, const void* gate, int gate_stride) {
     constexpr int S = NsTile<D>::kStride;
     const size_t smem = (size_t)(kTileQ + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -245,7 +249,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
     NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first, wide_weights,
-        mask_chunk, softcap, dk, dv);
+        mask_chunk, softcap, dk, dv, sink, (const __nv_bfloat16*)gate, gate_stride);
     NS_CHECK_LAUNCH("ns_attention_prefill");
     return NS_OK;
 }
@@ -258,11 +262,13 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 // `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
 // `mask_chunk`, `softcap`: see the top of the file (0: off); kept first keys and chunks do not go together.
 // `dv` > 0: values of that many features where the keys have `d` (both multiples of 8 then, the output rows nq * dv wide).
+// `sink` (optional, float [nq]): every query's denominator also holds exp(sink[h]), a term without key or value.
+// `gate` (optional, bfloat16, gate[token * gate_stride + h]): head h's output is multiplied by the sigmoid of its gate.
 NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                      const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
                                      const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                      int page_size, float scale, int window, int keep_first, int wide_weights, int mask_chunk, float softcap,
-                                     int dv, cudaStream_t stream) {
+                                     int dv, const float* sink, const void* gate, int gate_stride, cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
@@ -280,7 +286,7 @@ NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_
     case DD:                                                                                                         \
         return launch_prefill<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr,   \
                                   tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first, wide_weights, \
-                                  mask_chunk, softcap, d, dv);
+                                  mask_chunk, softcap, d, dv, sink, gate, gate_stride);
     switch (dmax) {
         NS_PREFILL_CASE(16) NS_PREFILL_CASE(32) NS_PREFILL_CASE(48) NS_PREFILL_CASE(64)
         NS_PREFILL_CASE(80) NS_PREFILL_CASE(96) NS_PREFILL_CASE(112) NS_PREFILL_CASE(128)
@@ -294,5 +300,5 @@ NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache
                                 const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                 int page_size, float scale, int window, cudaStream_t stream) {
     return ns_attention_prefill_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr, tiles, n_tiles,
-                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, 0, 0.f, 0, stream);
+                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, 0, 0.f, 0, nullptr, nullptr, 0, stream);
 }

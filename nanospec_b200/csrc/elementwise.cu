@@ -437,3 +437,80 @@ NS_API int ns_scale_softcap(float* x, int n_rows, int cols, long long stride, fl
     NS_CHECK_LAUNCH("ns_scale_softcap");
     return NS_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// The norm that takes no statistics (a "dynamic tanh"): out = tanh(alpha * x) * gain + bias, with one scalar alpha.
+// Fused with the residual sum like the norms above: x = resid (+ a) (+ b), the two optional branches in the output's
+// type; the sum is written back to the float stream unless rows are selected.  Everything is elementwise, so the grid is
+// (pieces of a row, rows) and a thread takes four neighbouring features where the rows start on 16 bytes.
+// `alpha` is read from device memory (it is a weight).
+// ---------------------------------------------------------------------------------------
+namespace {
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+add_dyt_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ gain,
+               const float* __restrict__ bias, const float* __restrict__ alpha, T* __restrict__ out,
+               const int* __restrict__ rows, int hidden, int write_resid) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int r = blockIdx.y;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const int e0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (e0 >= hidden) return;
+    const float al = *alpha;
+    float x[VEC];
+    if constexpr (VEC == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(resid + src + e0);
+        x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
+    } else {
+        x[0] = resid[src + e0];
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        if (a) x[i] += ns_ld(a, src + e0 + i);
+        if (b) x[i] += ns_ld(b, src + e0 + i);
+    }
+    if (write_resid && (a || b)) {
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(resid + src + e0) = make_float4(x[0], x[1], x[2], x[3]);
+        else resid[src + e0] = x[0];
+    }
+    T* o = out + (size_t)r * hidden + e0;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ns_st(o, i, fmaf(tanhf(al * x[i]), gain[e0 + i], bias ? bias[e0 + i] : 0.f));
+}
+
+template <typename T>
+int launch_add_dyt(float* resid, const void* a, const void* b, const float* gain, const float* bias, const float* alpha, void* out,
+                   const int* rows, int n_rows, int hidden, int write_resid, cudaStream_t stream) {
+    const bool vec = hidden % 4 == 0 && ((uintptr_t)resid % 16 == 0);
+    if (n_rows > 65535 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_add_dyt: %d rows", n_rows);
+    const int per = vec ? 4 : 1;
+    const int threads = 256;
+    const unsigned bx = (unsigned)((hidden + threads * per - 1) / (threads * per));
+    // the grid's y extent holds 65,535 rows: longer steps go in slices
+    for (int r0 = 0; r0 < n_rows; r0 += 65535) {
+        const int nr = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+        float* rs = rows ? resid : resid + (size_t)r0 * hidden;
+        const T* as = a && !rows ? (const T*)a + (size_t)r0 * hidden : (const T*)a;
+        const T* bs = b && !rows ? (const T*)b + (size_t)r0 * hidden : (const T*)b;
+        T* os = (T*)out + (size_t)r0 * hidden;
+        const int* rw = rows ? rows + r0 : nullptr;
+        if (vec) NS_LAUNCH((add_dyt_kernel<T, 4>), dim3(bx, nr), threads, 0, stream, rs, as, bs, gain, bias, alpha, os, rw, hidden, write_resid);
+        else NS_LAUNCH((add_dyt_kernel<T, 1>), dim3(bx, nr), threads, 0, stream, rs, as, bs, gain, bias, alpha, os, rw, hidden, write_resid);
+    }
+    NS_CHECK_LAUNCH("ns_add_dyt");
+    return NS_OK;
+}
+
+}  // namespace
+
+NS_API int ns_add_dyt(float* resid, const void* a, const void* b, const float* gain, const float* bias, const float* alpha, void* out,
+                      const int* rows, int n_rows, int hidden, int write_resid, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return NS_OK;
+    if (hidden <= 0 || !gain || !alpha) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_dyt: hidden=%d, a gain and alpha are needed", hidden);
+    if (rows && write_resid) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_dyt: a row selection cannot write the residual back");
+    if (dtype == NS_F32) return launch_add_dyt<float>(resid, a, b, gain, bias, alpha, out, rows, n_rows, hidden, write_resid, stream);
+    if (dtype == NS_BF16) return launch_add_dyt<__nv_bfloat16>(resid, a, b, gain, bias, alpha, out, rows, n_rows, hidden, write_resid, stream);
+    NS_FAIL(NS_ERR_ARGUMENT, "ns_add_dyt: unknown dtype %d", dtype);
+}

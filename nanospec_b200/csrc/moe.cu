@@ -13,7 +13,7 @@
 //   ns_moe_gather      x rows into that order;  ns_moe_combine   out[n] = sum_k weight[n, k] * y[row(n, k)] in float
 //   ns_moe_expert_rows the experts themselves for a few tokens, no host round trip: one block row per (token,
 //                      choice) streams the chosen expert's gate and up rows, then its down rows
-//   ns_activation      out = act(x) elementwise: exact (erf) gelu, tanh gelu, silu
+//   ns_activation      out = act(x) elementwise: exact (erf) gelu, tanh gelu, silu, squared relu
 #include "common.cuh"
 
 namespace {
@@ -283,6 +283,7 @@ moe_down_rows_kernel(const T* __restrict__ act, const int* __restrict__ ids, con
 __device__ __forceinline__ float act_value(float z, int kind) {
     if (kind == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
     if (kind == 1) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) { const float p = fmaxf(z, 0.f); return p * p; }
     return z / (1.f + expf(-z));
 }
 
@@ -415,10 +416,10 @@ NS_API int ns_moe_expert_rows(const void* x, const int* ids, const float* weight
     return NS_OK;
 }
 
-// kind 0: 0.5 z (1 + erf(z / sqrt 2));  1: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)));  2: z sigmoid(z)
+// kind 0: 0.5 z (1 + erf(z / sqrt 2));  1: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)));  2: z sigmoid(z);  3: max(z, 0)^2
 NS_API int ns_activation(const void* x, void* out, long long total, int kind, int dtype, cudaStream_t stream) {
     if (total <= 0) return NS_OK;
-    if (kind < 0 || kind > 2) NS_FAIL(NS_ERR_ARGUMENT, "ns_activation: unknown kind %d", kind);
+    if (kind < 0 || kind > 3) NS_FAIL(NS_ERR_ARGUMENT, "ns_activation: unknown kind %d", kind);
     if (total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) % 16 == 0)) {  // eight elements to a thread
         const size_t total8 = (size_t)total / 8;
         const unsigned vblocks = (unsigned)((total8 + 255) / 256);

@@ -408,6 +408,25 @@ NS_API int ns_delta_prepare(const void* proj, int ld_proj, const float* taps, in
     return NS_OK;
 }
 
+// The tail's move alone, for a mixer that runs a short convolution over the leading C channels of its projection in a
+// kernel of its own: after that kernel, every request's last n_taps - 1 inputs (in `state` at `tail_off`) move on by this
+// step's tokens.
+NS_API int ns_conv_tail(const void* proj, int ld_proj, float* state, long long state_floats, long long tail_off, const int* qo_indptr,
+                        const int* state_slot, int C, int n_taps, int n_requests, int dtype, cudaStream_t stream) {
+    if (n_requests <= 0 || n_taps <= 1 || C <= 0) return NS_OK;
+    const dim3 grid(n_requests, (C + 255) / 256);
+    if (dtype == NS_F32)
+        NS_LAUNCH((conv_tail_kernel<float>), grid, 256, 0, stream, (const float*)proj, ld_proj, state, state_floats, tail_off, qo_indptr,
+                  state_slot, C, n_taps);
+    else if (dtype == NS_BF16)
+        NS_LAUNCH((conv_tail_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)proj, ld_proj, state, state_floats,
+                  tail_off, qo_indptr, state_slot, C, n_taps);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_conv_tail: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_conv_tail");
+    return NS_OK;
+}
+
 NS_API int ns_rotary_prepare(const void* proj, int ld_proj, const int* positions, const int* token_req, const float* inv_freq,
                              float magnitude, int interleaved, int rot_pairs, float* rec, int ld_rec, int n_tokens, int H, int D,
                              int Dp, int V, float q_scale, float k_scale, int dtype, cudaStream_t stream) {

@@ -434,13 +434,15 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: t
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       token_req: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, nq: int, nkv: int,
                       head_dim: int, page_size: int, scale: float | None = None, window: int = 0,
-                      keep_first: int = 0, v_dim: int | None = None, chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
+                      keep_first: int = 0, v_dim: int | None = None, chunk: int = 0, softcap: float = 0.0,
+                      sink: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
     """q: [N, >= nq*head_dim] rows (a view into the packed projection is fine, unit inner
     stride); out: [N, nq*v_dim] (`v_dim`: the values' head size when it differs from the keys').  `keep_first`: the
     first so many keys of a request stay visible behind the window.  `chunk` > 0: a query sees only the keys of its own
-    chunk of that many positions; `softcap` > 0: scaled scores pass through softcap * tanh(s / softcap).  See
-    csrc/attention_generic.cu for the masking rule."""
-    _cuda(q, k_cache, v_cache, block_table, token_req, positions, out)
+    chunk of that many positions; `softcap` > 0: scaled scores pass through softcap * tanh(s / softcap).  `sink` and
+    `gate`: see `attention`.  See csrc/attention_generic.cu for the masking rule."""
+    _cuda(q, k_cache, v_cache, block_table, token_req, positions, out, sink, gate)
+    _check_sink_gate(sink, gate, nq, n_rows=out.shape[0], dtype=q.dtype)
     _i32(positions, "positions"), _i32(token_req, "token_req")
     n = out.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[0] != n or q.dtype != out.dtype:
@@ -449,11 +451,19 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         raise KernelError("attention: the cache must hold the activations' dtype")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    lib.call("ns_attention_generic", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+    lib.call("ns_attention_generic_sink", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(), positions.data_ptr(),
              out.data_ptr(), out.stride(0), n, nq, nkv, head_dim, int(v_dim or head_dim), page_size, float(scale), int(window),
-             int(keep_first), int(chunk), float(softcap), dtype_code(q.dtype), _stream())
+             int(keep_first), int(chunk), float(softcap), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             dtype_code(q.dtype), _stream())
     return out
+
+
+def _check_sink_gate(sink: torch.Tensor | None, gate: torch.Tensor | None, nq: int, n_rows: int, dtype: torch.dtype) -> None:
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous()):
+        raise KernelError("attention: the sink is one contiguous float32 number per query head")
+    if gate is not None and (gate.dtype != dtype or gate.dim() != 2 or gate.shape[0] != n_rows or gate.shape[1] < nq or gate.stride(1) != 1):
+        raise KernelError("attention: the gate is one number per token and query head, in the activations' dtype, unit inner stride")
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
@@ -532,7 +542,8 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
                      work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0, wide_weights: bool = False,
-                     chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None) -> None:
+                     chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None, sink: torch.Tensor | None = None,
+                     gate: torch.Tensor | None = None) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
@@ -549,7 +560,8 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
     # (kept first keys behind a window, chunks and capped scores are the cp.async kernel's: the TMA kernel loads whole
     # pages in key order and knows one mask)
     if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0 \
-            and not keep_first and not wide_weights and not chunk and not softcap and v_dim == head_dim:
+            and not keep_first and not wide_weights and not chunk and not softcap and v_dim == head_dim \
+            and sink is None and gate is None:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
         if work is not None and window == 0:
             ws = ctx.workspace
@@ -585,7 +597,8 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
-             int(keep_first), int(bool(wide_weights)), int(chunk), float(softcap), n_splits, int(v_dim), _stream())
+             int(keep_first), int(bool(wide_weights)), int(chunk), float(softcap), n_splits, int(v_dim), _ptr(sink), _ptr(gate),
+             gate.stride(0) if gate is not None else 0, _stream())
 
 
 PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
@@ -593,14 +606,15 @@ PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whateve
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0,
-                      wide_weights: bool = False, chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None) -> None:
+                      wide_weights: bool = False, chunk: int = 0, softcap: float = 0.0, v_dim: int | None = None,
+                      sink: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu), also values of
     another width than the keys (`v_dim`, both multiples of 8)."""
     v_dim = head_dim if v_dim is None else v_dim
     if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 and not wide_weights \
-            and not chunk and not softcap and v_dim == head_dim \
+            and not chunk and not softcap and v_dim == head_dim and sink is None and gate is None \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         # heads of 64: two query heads of a kv head to a block (four softmax warps per sub-partition keep the exponential
         # unit busier and the keys are read once for both) - once one head to a block would give more blocks than SMs
@@ -615,7 +629,8 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
     lib.call("ns_attention_prefill_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
-             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), int(chunk), float(softcap), int(v_dim), _stream())
+             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), int(chunk), float(softcap), int(v_dim),
+             _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
 
 
 def _attention_plan(ctx) -> dict:
@@ -652,7 +667,7 @@ def _attention_plan(ctx) -> dict:
 
 def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
               window: int = 0, keep_first: int = 0, v_dim: int | None = None, wide_weights: bool = False, chunk: int = 0,
-              softcap: float = 0.0) -> torch.Tensor:
+              softcap: float = 0.0, sink: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
 
     bfloat16 with a head size that the tensor-core kernels take: the decode kernel for requests
@@ -660,14 +675,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     with about 16 bits each (two bfloat16 products per weight) instead of 8, for designs that state their weights in
     float32; the m16n8k16 kernels have it.  `chunk` > 0: a query sees only the keys of its own chunk of that many
     positions, counted from the start of the sequence; `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the exact and
-    the m16n8k16 kernels); `v_dim`: values of another width than the keys (the same kernels, widths in multiples of 8).  float32, and head sizes those
-    kernels refuse: the exact kernel, one warp per (token, head)."""
+    the m16n8k16 kernels); `v_dim`: values of another width than the keys (the same kernels, widths in multiples of 8).
+    `sink` (float32 [nq]): the softmax's denominator also holds exp(sink[h]), a term that has no key and no value and counts once
+    (zeros: "one added to the denominator"); `gate` ([N, >= nq] in the activations' dtype, a column range of the packed projection
+    is fine): head h's output is multiplied by sigmoid(gate[n, h]).  Both run in the exact and the m16n8k16 kernels.  float32, and head
+    sizes those kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim
     keep_first = keep_first if window else 0
     if not _tensor_core_attention(qkv.dtype, head_dim, v_dim) or nq // nkv > 64 or (v_dim != head_dim and (nq * head_dim) % 8):
         return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
-                                 head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim, chunk, softcap)
-    _cuda(qkv, out, lane.k, lane.v, lane.block_table)
+                                 head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim, chunk, softcap, sink, gate)
+    _cuda(qkv, out, lane.k, lane.v, lane.block_table, sink, gate)
+    _check_sink_gate(sink, gate, nq, n_rows=out.shape[0], dtype=qkv.dtype)
     if out.stride(1) != 1 or qkv.stride(1) != 1 or lane.k.dtype != qkv.dtype:
         raise KernelError("attention: row-major bfloat16 operands and a bfloat16 cache are needed")
     plan = _attention_plan(ctx)
@@ -681,18 +700,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         fork, join = _side_events(qkv.device)
         fork.record(main)
         side.wait_event(fork)
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim, sink, gate)
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim)
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim, sink, gate)
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim)
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights, chunk, softcap, v_dim, sink, gate)
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights, chunk, softcap, v_dim, sink, gate)
     return out
 
 
@@ -980,11 +999,11 @@ def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: t
     return out
 
 
-ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
-    """out = act(x) elementwise in float, rounded once: "gelu_erf" (the exact gelu), "gelu_tanh", "silu"."""
+    """out = act(x) elementwise in float, rounded once: "gelu_erf" (the exact gelu), "gelu_tanh", "silu", "relu2" (the square of relu)."""
     _cuda(x, out)
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation: unknown kind {kind!r} (known: {', '.join(ACTIVATIONS)})")
@@ -1161,3 +1180,88 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
         raise KernelError("add_bias: rows with a unit inner stride and a float32 bias of their width")
     lib.call("ns_add_bias", x.data_ptr(), x.stride(0), bias.data_ptr(), x.shape[0], x.shape[1], dtype_code(x.dtype), _stream())
     return x
+
+
+# ---- a norm without statistics; attention whose q and k are prepared head by head -------------------------------------
+
+def add_dyt(resid: torch.Tensor, branches, gain: torch.Tensor, bias: torch.Tensor | None, alpha: torch.Tensor, out: torch.Tensor,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
+    """resid (+= each of up to two `branches`); out = tanh(alpha * resid) * gain + bias, elementwise in float32 and rounded once
+    (csrc/elementwise.cu).  `alpha` is a float32 tensor of one element on the device.  With `rows`, output row j reads input row
+    rows[j] and the residual is left unchanged."""
+    branches = [b for b in (branches or ()) if b is not None]
+    if len(branches) > 2:
+        raise KernelError("add_dyt: at most two branches")
+    _cuda(resid, gain, bias, alpha, out, rows, *branches)
+    _i32(rows, "rows")
+    hidden, n_rows = resid.shape[1], out.shape[0]
+    if resid.dtype != torch.float32 or gain.dtype != torch.float32 or alpha.dtype != torch.float32 or alpha.numel() != 1 \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != hidden or not bias.is_contiguous())):
+        raise KernelError("add_dyt: the residual stream, the gain, the bias and alpha are float32")
+    if not (resid.is_contiguous() and out.is_contiguous() and gain.is_contiguous()) or out.shape[1] != hidden or gain.numel() != hidden:
+        raise KernelError("add_dyt: operands must be contiguous and agree on the width")
+    for b in branches:
+        if b.dtype != out.dtype or b.shape != resid.shape or not b.is_contiguous():
+            raise KernelError("add_dyt: a branch must match the residual's shape and the output's dtype")
+    if (rows is None and n_rows != resid.shape[0]) or (rows is not None and rows.numel() != n_rows):
+        raise KernelError("add_dyt: one output row per residual row, or per selected row")
+    a = branches[0] if branches else None
+    b = branches[1] if len(branches) > 1 else None
+    lib.call("ns_add_dyt", resid.data_ptr(), _ptr(a), _ptr(b), gain.data_ptr(), _ptr(bias), alpha.data_ptr(), out.data_ptr(), _ptr(rows),
+             n_rows, hidden, int(rows is None), dtype_code(out.dtype), _stream())
+    return out
+
+
+def head_prepare_store(proj: torch.Tensor, out: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int, v_dim: int, *,
+                       inv_freq: torch.Tensor | None = None, magnitude: float = 1.0, interleaved: bool = False,
+                       norm: str | None = None, q_gain: torch.Tensor | None = None, k_gain: torch.Tensor | None = None,
+                       eps: float = 0.0, q_temp: tuple[float, float] | None = None, taps: torch.Tensor | None = None,
+                       v_from_k: bool = False, write_kv: bool = True) -> None:
+    """Rows [q: nq*head_dim | k: nkv*head_dim | v: nkv*v_dim] of `proj` (no v part when `v_from_k`: the values are the keys as
+    projected), head by head (csrc/head_prepare.cu): a causal convolution over time per channel (`taps` [channels, n] float32; the
+    last n - 1 inputs of every request live in `lane.state` and move on by this step's tokens), an RMS norm per head (`norm`
+    "before" or "after" the rotation; gains [head_dim] float32 shared by the heads, or none), the rotation of the first
+    2 * len(inv_freq) features (pairs (2i, 2i+1) when `interleaved`, (i, i + len) otherwise; cos and sin times `magnitude`), the
+    queries times 1 + coef * ln(floor((position + 1) / every) + 1) for `q_temp` = (coef, every).  q and k go to `out` (which may be
+    `proj` itself when there is no convolution), k and v to the tokens' cache slots when `write_kv`."""
+    _cuda(proj, out, inv_freq, q_gain, k_gain, taps)
+    cols = nq * head_dim + nkv * head_dim + (0 if v_from_k else nkv * v_dim)
+    if proj.stride(1) != 1 or out.stride(1) != 1 or proj.shape[1] < cols or out.shape[1] < (nq + nkv) * head_dim \
+            or proj.dtype != out.dtype or proj.shape[0] != out.shape[0]:
+        raise KernelError("head_prepare_store: rows of [q | k | v] with unit inner stride, in and out of one dtype")
+    for t, name, size in ((inv_freq, "inv_freq", None), (q_gain, "q_gain", head_dim), (k_gain, "k_gain", head_dim)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or (size is not None and t.numel() != size)):
+            raise KernelError(f"head_prepare_store: {name} must be contiguous float32" + (f" of {size} entries" if size else ""))
+    if norm not in (None, "before", "after"):
+        raise KernelError(f"head_prepare_store: norm {norm!r} (None, 'before' or 'after' the rotation)")
+    n_taps = 1
+    state = None
+    if taps is not None:
+        n_taps = int(taps.shape[1])
+        state = lane.state
+        if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.shape[0] != cols:
+            raise KernelError("head_prepare_store: float32 taps, one row per channel of [q | k | v]")
+        if n_taps > 1 and (state is None or state.dtype != torch.float32 or not state.is_contiguous()
+                           or state[0].numel() < (n_taps - 1) * cols):
+            raise KernelError("head_prepare_store: the convolution's last inputs need a float32 state of (taps - 1) * channels per slot")
+        if n_taps > 1 and proj.data_ptr() == out.data_ptr():
+            raise KernelError("head_prepare_store: a convolution cannot run in place")
+    if write_kv:
+        if lane.k is None or lane.v is None or lane.k.dtype != proj.dtype or lane.v.dtype != proj.dtype \
+                or not (lane.k.is_contiguous() and lane.v.is_contiguous()):
+            raise KernelError("head_prepare_store: cache pages must be contiguous and of the activations' dtype")
+        if lane.k.shape[-1] != head_dim or lane.v.shape[-1] != v_dim:
+            raise KernelError("head_prepare_store: the cache's head sizes are not the mixer's")
+    bt = lane.block_table if write_kv else None
+    coef, every = (float(q_temp[0]), float(q_temp[1])) if q_temp else (0.0, 0.0)
+    state_floats = state.stride(0) if state is not None and n_taps > 1 else 0
+    lib.call("ns_head_prepare_store", proj.data_ptr(), proj.stride(0), out.data_ptr(), out.stride(0), ctx.positions.data_ptr(),
+             ctx.token_req.data_ptr(), ctx.qo_indptr.data_ptr(), ctx.state_slot.data_ptr(), _ptr(bt), bt.stride(0) if bt is not None else 0,
+             _ptr(inv_freq), float(magnitude), int(bool(interleaved)), inv_freq.numel() if inv_freq is not None else 0, _ptr(q_gain),
+             _ptr(k_gain), {None: 0, "before": 1, "after": 2}[norm], float(eps), coef, every, _ptr(taps), n_taps,
+             _ptr(state) if n_taps > 1 else None, state_floats, _ptr(lane.k) if write_kv else None, _ptr(lane.v) if write_kv else None,
+             lane.page_size, nq, nkv, head_dim, v_dim, int(bool(v_from_k)), proj.shape[0], int(bool(write_kv)), dtype_code(proj.dtype),
+             _stream())
+    if n_taps > 1:
+        lib.call("ns_conv_tail", proj.data_ptr(), proj.stride(0), state.data_ptr(), state_floats, 0, ctx.qo_indptr.data_ptr(),
+                 ctx.state_slot.data_ptr(), cols, n_taps, ctx.n_requests, dtype_code(proj.dtype), _stream())

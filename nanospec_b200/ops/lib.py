@@ -50,8 +50,14 @@ _SIGNATURES: dict[str, list] = {
     "ns_gemm_bf16_tc_gated": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ns_attention_prefill_tc": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "ns_wait_probe": [_P, _L, _P, _P],
-    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _I, _I, _P],
-    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _I, _P],
+    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _I, _I,
+                                 _P, _P, _I, _P],
+    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _F, _I, _P, _P, _I, _P],
+    "ns_attention_generic_sink": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P, _I, _I, _P],
+    "ns_add_dyt": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ns_head_prepare_store": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _F, _I, _I, _P, _P, _I, _F, _F, _F, _P, _I, _P, _L, _P, _P,
+                              _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ns_conv_tail": [_P, _I, _P, _L, _L, _P, _P, _I, _I, _I, _I, _P],
     "ns_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "ns_stream_mix_norm": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
     "ns_stream_read": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

@@ -25,6 +25,11 @@ then, when the layer has one, x = x + norm(side_input(x)) (`LayerSpec.params["si
 "side_input" slot; checkpoint sub-prefix under the slot name "side_input").  The sublayers read the stream itself, so
 nothing stays pending: one kernel (`ops.norm_add`) norms the branch, adds it to the float32 stream and leaves the
 stream's copy in the compute type for the next sublayer; the block hands that copy on as a `StreamCopy`.
+
+"parallel" has one norm and both sublayers read its output: h = norm(x); x = x + (mixer(h) + feed_forward(h)).  Neither branch is
+added by a kernel of its own when the norm that comes next takes two pending branches (`takes_branches`, as the "dyt" norm does):
+the block leaves the pair pending and that norm's kernel sums stream, mixer branch and feed-forward branch in float32.  Otherwise the
+mixer's branch joins the stream through `ops.residual_add` and the feed-forward's stays pending as a tensor.
 """
 
 from __future__ import annotations
@@ -163,3 +168,51 @@ class OutNormBlock:
               out_name: str = "final_normed") -> torch.Tensor:
         """The model's end: nothing is pending, the final norm reads the stream; only `rows` when given."""
         return norm.add_norm(resid, None, ctx, rows=rows, out_name=out_name)
+
+
+@register_part("block", "parallel")
+class ParallelBlock:
+    slots = ("norm_mixer", "mixer", "feed_forward")
+    takes_follow = True
+
+    def __init__(self, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
+        self.layer = layer
+        self.mixer = build_part("mixer", layer.mixer, dtype, device)
+        self.norm_mixer = build_part("norm", layer.norm, dtype, device)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device) if layer.feed_forward is not None else None
+
+    def parts(self) -> dict:
+        return {s: getattr(self, s) for s in self.slots if getattr(self, s) is not None}
+
+    def takes_pair(self) -> bool:
+        """Whether this block's norm sums two pending branches into the stream itself."""
+        return int(getattr(self.norm_mixer, "takes_branches", 1)) >= 2
+
+    @staticmethod
+    def _settle(resid: torch.Tensor, pending):
+        """A pending pair as one pending tensor: the first branch joins the stream now."""
+        if isinstance(pending, tuple):
+            ops.residual_add(resid, pending[0])
+            return pending[1]
+        return pending
+
+    def forward(self, resid: torch.Tensor, pending, ctx: StepContext, lane: LaneView, writes: bool = True, follow=None):
+        if isinstance(pending, tuple) and not self.takes_pair():
+            pending = self._settle(resid, pending)
+        h = self.norm_mixer.add_norm(resid, pending, ctx)
+        a = self.mixer.forward(h, ctx, lane, writes)
+        if self.feed_forward is None:
+            return resid, a
+        # the pair stays pending only for a norm that is known to take it: the next block's, when that is of this kind
+        pair = getattr(self.feed_forward, "names_output", False) and isinstance(follow, ParallelBlock) and follow.takes_pair()
+        if pair:
+            return resid, (a, self.feed_forward.forward(h, ctx, out_name="branch_ff"))
+        ops.residual_add(resid, a)
+        return resid, self.feed_forward.forward(h, ctx)
+
+    def close(self, resid: torch.Tensor, pending, norm, ctx: StepContext, rows: torch.Tensor | None = None,
+              out_name: str = "final_normed") -> torch.Tensor:
+        """The model's end: the final norm takes what is pending."""
+        if isinstance(pending, tuple) and int(getattr(norm, "takes_branches", 1)) < 2:
+            pending = self._settle(resid, pending)
+        return norm.add_norm(resid, pending, ctx, rows=rows, out_name=out_name)

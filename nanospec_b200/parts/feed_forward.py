@@ -68,8 +68,11 @@ class SwiGLU(Part):
 @register_part("feed_forward", "dense_act")
 class DenseAct(Part):
     """down(act(up(x))), no gate, no biases.  params: hidden, intermediate, activation ("gelu_erf": the exact gelu,
-    "gelu_tanh", "silu"), names (optional: keys "up", "down"; default "up", "down").  The activation is float32 on the
-    rounded product and is rounded once."""
+    "gelu_tanh", "silu", "relu2": the square of relu), names (optional: keys "up", "down"; default "up", "down").  The activation is float32 on the
+    rounded product and is rounded once.  `forward` takes `out_name`, the step buffer that receives the result (an arrangement that
+    holds two branches at once gives another name than the mixers' "branch")."""
+
+    names_output = True
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
@@ -88,7 +91,7 @@ class DenseAct(Part):
     def bind(self, tensors) -> None:
         self.w_up, self.w_down = tensors[self.n_up].contiguous(), tensors[self.n_down].contiguous()
 
-    def forward(self, x, ctx: StepContext):
+    def forward(self, x, ctx: StepContext, out_name: str = "branch"):
         u = ops.linear(x, self.w_up, ctx.buffer("ffn_up", self.inter))
         a = ops.activation(u, ctx.buffer("ffn_act", self.inter), self.activation)
-        return ops.linear(a, self.w_down, ctx.buffer("branch", self.hidden))
+        return ops.linear(a, self.w_down, ctx.buffer(out_name, self.hidden))

@@ -96,3 +96,45 @@ class LayerNorm(RMSNorm):
         if self.bias is not None:  # the kernel of the streams, on one stream: the residual sum, the norm and its bias
             return ops.stream_mix_norm(resid, 1, pending, None, None, None, self.gain, self.bias, self.eps, True, out, rows=rows)
         return ops.add_layernorm(resid, pending, self.gain, self.eps, out, rows=rows)
+
+
+@register_part("norm", "dyt")
+class DynamicTanh(Part):
+    """tanh(alpha * x) * gain + bias: a norm that takes no mean and no variance (one scalar `alpha` stored beside the gain and
+    the bias), elementwise in float32 over the float32 stream and rounded once.  It is not a per-row scale, so it offers no `sink`
+    and is never folded into the products around it.  `add_norm` also takes a tuple of two pending branches (what a block that
+    runs its sublayers side by side leaves).  params: hidden, weight_name (default "weight"), bias_name (default weight_name +
+    ".b"), alpha_name (default weight_name + ".alpha"); names follow the norm's prefix directly."""
+
+    sink = None
+    centered = False
+    takes_branches = 2  # `add_norm` accepts a tuple of so many pending branches
+
+    def __init__(self, spec, dtype, device) -> None:
+        super().__init__(spec, dtype, device)
+        self.hidden = int(spec["hidden"])
+        self.weight_name = spec.params.get("weight_name", "weight")
+        self.bias_name = spec.params.get("bias_name", self.weight_name + ".b")
+        self.alpha_name = spec.params.get("alpha_name", self.weight_name + ".alpha")
+        self.gain: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+        self.alpha: torch.Tensor | None = None
+
+    def weight_specs(self) -> dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.hidden,), rule="float32", init="gain"),
+                self.bias_name: WeightSpec((self.hidden,), rule="float32", init="normal", std=0.1),
+                self.alpha_name: WeightSpec((), rule="float32", init="gain")}
+
+    def bind(self, tensors) -> None:
+        self.gain = tensors[self.weight_name].contiguous()
+        self.bias = tensors[self.bias_name].contiguous()
+        self.alpha = tensors[self.alpha_name].reshape(1).contiguous()
+
+    def add_norm(self, resid: torch.Tensor, pending, ctx: StepContext,
+                 rows: torch.Tensor | None = None, out_name: str = "normed"):
+        if isinstance(pending, ops.RowScaled):
+            raise ValueError("a RowScaled reached a norm that cannot take it")
+        branches = pending if isinstance(pending, (tuple, list)) else (pending,)
+        n = resid.shape[0] if rows is None else rows.numel()
+        out = ctx.buffer(out_name, self.hidden, rows=n)
+        return ops.add_dyt(resid, branches, self.gain, self.bias, self.alpha, out, rows=rows)
