@@ -1,5 +1,5 @@
-"""nanospec_b200: a small, whole, single-GPU inference engine for the Llama 3 dense decoder (and two further decoders
-built from the same parts, Dezolorn and Sorizen) on NVIDIA B200 (sm_100a): typed configuration and registry, safetensors weights, layers
+"""nanospec_b200: a small, whole, single-GPU inference engine for the Llama 3 dense decoder (and further decoders
+built from the same parts: Dezolorn, Sorizen, Debuvik and Fubolix) on NVIDIA B200 (sm_100a): typed configuration and registry, safetensors weights, layers
 assembled from parts, a paged cache manager, one step function for mixed batches, a
 continuous-batching scheduler, sampling, trace replay, and hand-written CUDA kernels.
 

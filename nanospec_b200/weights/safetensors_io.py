@@ -116,7 +116,7 @@ def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor], metada
         fh.write(blob)
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
-            fh.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            fh.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
 
 
 def iter_model_files(folder: str | Path) -> Iterator[Path]:

@@ -12,12 +12,15 @@ import math
 import torch
 
 F = torch.float64
-ROUND = None  # a dtype: activations pass through it wherever a 16-bit pipeline would store them
+ROUND = None  # a dtype, or a function of a tensor: activations pass through it wherever a 16-bit pipeline would store them
+SINK = True   # False: the softmax without its sink (to show that a test would notice a sink left out)
 
 
 def r(t):
     """What a reduced-precision pipeline keeps of an activation; the identity unless `ROUND` is set."""
-    return t if ROUND is None else t.to(ROUND).to(F)
+    if ROUND is None:
+        return t
+    return ROUND(t) if callable(ROUND) else t.to(ROUND).to(F)
 
 
 def dynamic_tanh(x, w, b, alpha):
@@ -104,7 +107,7 @@ def softmax_with_sink(s, mask, sink):
     s = s.masked_fill(~mask[None], -math.inf)
     top = torch.maximum(s.max(-1, keepdim=True).values, sink[:, None, None])
     e = torch.exp(s - top)
-    return e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None, None] - top))
+    return e / (e.sum(-1, keepdim=True) + (torch.exp(sink[:, None, None] - top) if SINK else 0.0))
 
 
 def attend(q, k, v, scale, mask, sink):
@@ -176,7 +179,7 @@ def forward(cfg: dict, weights: dict, tokens, rounded=None, layers_out: list | N
     global ROUND
     ROUND = rounded
     try:
-        W = {k: v.to(F) for k, v in weights.items()}
+        W = {k: torch.as_tensor(v).to(F) for k, v in weights.items()}
         eps = float(cfg["norm"]["eps"])
         ids = torch.as_tensor(tokens, dtype=torch.long)
         positions = torch.arange(len(ids))
