@@ -30,7 +30,10 @@ over a cached latent with a sink or a gate, hyper-connections, dense and routed 
 windowed attention layers alone, and `--design debuvik` for Debuvik models (latent attention with a gate on every output
 feature, chunked attention with capped scores and biases, partly on an earlier layer's keys and values, norms on the sublayers'
 outputs, the token's side input) beside Dezolorn layers of windowed attention and Sorizen layers of latent attention; `like`
-sets every Debuvik kernel's fraction of its bound over that of the sibling's kernel that does the like work.
+sets every Debuvik kernel's fraction of its bound over that of the sibling's kernel that does the like work.  `--design fubolix`:
+Fubolix models (one dynamic-tanh norm a layer whose output the mixer and a squared-relu feed-forward both read; attention with a
+sink in the denominator - windowed with kept first keys, gated heads and keys as values; with a query temperature; behind a short
+convolution) beside Dezolorn layers of windowed attention.
 """
 
 from __future__ import annotations
@@ -895,6 +898,128 @@ def run_design_debuvik(args) -> dict:
     }
 
 
+# ---- Fubolix beside Dezolorn attention layers (--design fubolix) -------------------------------------------------------------
+
+FUBOLIX_SIZES = {
+    # width, feed-forward, heads / kv heads / head size, layers (in the pattern windowed, convolved, windowed, tempered)
+    "w2048": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, layers=8),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, layers=4),
+}
+FUBOLIX_CONV, FUBOLIX_TEMP_EVERY = 4, 64
+
+
+def fubolix_config(sz: dict) -> dict:
+    d = sz["dim"]
+    yarn = {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}
+    base = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5}
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    windowed = {"type": "attention", "mlp": mlp, "mixer": {**base, "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
+                                                            "rot": {"dims": d // 2, "base": 1000000.0, "scaling": yarn}}}
+    convolved = {"type": "attention_3", "mlp": mlp, "mixer": {**base, "conv": FUBOLIX_CONV, "rot": {"dims": d, "base": 1000000.0, "scaling": yarn}}}
+    tempered = {"type": "attention_2", "mlp": mlp, "mixer": {**base, "q_temp": {"coef": 0.3, "every": FUBOLIX_TEMP_EVERY}}}
+    pattern = [windowed, convolved, windowed, tempered]
+    return {"architecture": "Fubolix", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+            "layers": [pattern[i % 4] for i in range(sz["layers"])]}
+
+
+def fubolix_sibling(sz: dict) -> dict:
+    """The closest model the framework had: Dezolorn layers of windowed attention with kept first keys alone (layer norm, q/k norm,
+    rotation with scaling, the same m16n8k16 attention kernels), at the same width, feed-forward width, heads and layer count."""
+    cfg = windowed_sibling(sz)
+    for layer in cfg["layers"]:
+        layer["mixer"] = {**layer["mixer"], "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP}}
+    return cfg
+
+
+def fubolix_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, pk: dict) -> dict[str, float]:
+    """Seconds that every kernel of one step needs at least, over all its calls (see kernel_bounds)."""
+    N = tokens or batch
+    W, L, H, nkv, d = sz["width"], sz["layers"], sz["heads"], sz["kv_heads"], sz["dim"]
+    bw, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    seen_w = lambda p: min(p + 1, DESIGN_WINDOW) + max(0, min(DESIGN_KEEP, p + 1 - DESIGN_WINDOW))
+    pairs_w = sum(seen_w(p) for p in range(tokens)) if tokens else batch * seen_w(context)
+    pairs_all = tokens * (tokens + 1) // 2 if tokens else batch * (context + 1)
+    out: dict[str, float] = {}
+    if kind == "dezolorn":
+        out["ns_add_layernorm"] = 2 * L * 12.0 * N * W / bw
+        out["ns_qk_norm_rope_store"] = L * 2.0 * N * ((H + nkv) * d * 2 + nkv * d + 2 * nkv * d) / bw
+        if tokens:
+            out["ns_attention_prefill_kept"] = L * 4.0 * H * d * pairs_w / tc
+        else:
+            out["ns_attention_decode_kept"] = L * 4.0 * pairs_w * nkv * d / bw
+        out["ns_swiglu"] = L * 6.0 * N * sz["ff"] / bw
+        return out
+    n_win = sum(1 for i in range(L) if i % 4 in (0, 2))
+    n_all = L - n_win
+    # one norm a layer: the stream read and written in float32, two branches read and the result written in bfloat16 (the first
+    # has no branches yet); the model's last norm reads the wanted rows only
+    out["ns_add_dyt"] = ((L - 1) * 14.0 + 6.0) * N * W / bw
+    # projections read and q, k written back, k and v to the cache; a windowed layer has no v to read
+    out["ns_head_prepare_store"] = 2.0 * N * (L * ((H + nkv) * d * 2 + 2 * nkv * d) + n_all * nkv * d) / bw
+    if tokens:
+        out["ns_attention_prefill_kept"] = 4.0 * H * d * (n_win * pairs_w + n_all * pairs_all) / tc
+    else:
+        out["ns_attention_decode_kept"] = 4.0 * (n_win * pairs_w + n_all * pairs_all) * nkv * d / bw
+    out["ns_activation"] = L * 4.0 * N * sz["ff"] / bw
+    out["ns_residual_add"] = 10.0 * N * W / bw
+    out["ns_embed_streams"] = 6.0 * N * W / bw
+    return out
+
+
+def run_design_fubolix(args) -> dict:
+    import torch
+
+    from nanospec_b200 import random_model
+
+    pk, pk_src = peaks()
+    out_sizes = {}
+    for name, sz in FUBOLIX_SIZES.items():
+        row = {}
+        for kind in ("fubolix", "dezolorn"):
+            cfg = fubolix_config(sz) if kind == "fubolix" else fubolix_sibling(sz)
+            model = random_model(cfg, seed=1, device="cuda", dtype=torch.bfloat16)
+            pages_per_req = -(-(CONTEXT + args.repeats * args.steps + args.warmup + 64) // PAGE)
+            eng = design_engine(model, 64, max(64 * pages_per_req, -(-PREFILL_TOKENS // PAGE) + 8) + 8)
+            rec = {}
+            for b in (8, 64):
+                pt = time_decode(eng, b, args.steps, args.warmup, args.repeats)
+                rec[f"decode_b{b}_tok_s"] = round(b * 1000.0 / pt["ms"], 1)
+                rec[f"decode_b{b}_ms"] = round(pt["ms"], 4)
+                rec[f"decode_b{b}_clocks"] = {"sm_mhz": pt["clocks"].get("sm_mhz"), "reasons": pt["clocks"].get("reasons")}
+                if b == 8 and kind == "fubolix" and name == "w4096":
+                    headline = pt
+            pre_ms, pre_clocks = time_prefill(eng, warmup=3, iters=5)
+            rec["prefill_tok_s"] = round(PREFILL_TOKENS * 1000.0 / pre_ms, 1)
+            rec["prefill_ms"] = round(pre_ms, 3)
+            rec["prefill_clocks"] = {"sm_mhz": pre_clocks.get("sm_mhz"), "reasons": pre_clocks.get("reasons")}
+            del eng
+            torch.cuda.empty_cache()
+            kernels = {}
+            for what, tokens, batch in (("prefill", PREFILL_TOKENS, 0), ("decode_b64", 0, 64)):
+                timed = time_kernels(model, tokens, batch, CONTEXT)
+                bounds = fubolix_bounds(kind, sz, tokens, batch, CONTEXT, pk)
+                kernels[what] = {k: {"calls": n, "ms": round(ms, 4), "bound_ms": round(bounds[k] * 1e3, 4) if k in bounds else None,
+                                     "frac": round(bounds[k] * 1e3 / ms, 4) if k in bounds and ms > 0 else None}
+                                 for k, (n, ms) in sorted(timed.items(), key=lambda kv: -kv[1][1])}
+            rec["kernels"] = kernels
+            row[kind] = rec
+            del model
+            torch.cuda.empty_cache()
+        out_sizes[name] = row
+    value = out_sizes["w4096"]["fubolix"]["decode_b8_tok_s"]
+    return {
+        "metric": "decode tok/s (Fubolix, width 4,096, 4 layers, batch 8, 1,024-token context)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": out_sizes["w4096"]["fubolix"]["decode_b8_ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform random token ids, random weights",
+        "config": {"design": "fubolix beside dezolorn (attention layers)", "sizes": FUBOLIX_SIZES, "vocab": DESIGN_VOCAB,
+                   "window": DESIGN_WINDOW, "keep_first": DESIGN_KEEP, "conv": FUBOLIX_CONV, "seq_len": CONTEXT,
+                   "prefill_tokens": PREFILL_TOKENS, "page": PAGE, "cuda_graphs": True, "peaks": pk_src,
+                   "l2": "the weights of every step are larger than L2"},
+        "gpu_launches": headline["launches"], "clocks": headline["clocks"], "sizes": out_sizes,
+    }
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
 
@@ -911,7 +1036,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"])
     ap.add_argument("--no-workloads", action="store_true", help="leave out the 3B continuous-batching and 1B mixed workloads")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--design", choices=["dezolorn", "sorizen", "debuvik"], help="measure this design beside its closest sibling of equal size instead")
+    ap.add_argument("--design", choices=["dezolorn", "sorizen", "debuvik", "fubolix"], help="measure this design beside its closest sibling of equal size instead")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.repeats = max(1, args.repeats)
@@ -919,7 +1044,7 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
-    out = run_reference(args) if args.impl == "reference" else run_design_sorizen(args) if args.design == "sorizen" else run_design_debuvik(args) if args.design == "debuvik" else run_design(args) if args.design else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else run_design_fubolix(args) if args.design == "fubolix" else run_design_sorizen(args) if args.design == "sorizen" else run_design_debuvik(args) if args.design == "debuvik" else run_design(args) if args.design else run_ours(args)
     print(json.dumps(out), flush=True)
     return 0
 

@@ -442,7 +442,7 @@ NS_API int ns_scale_softcap(float* x, int n_rows, int cols, long long stride, fl
 // The norm that takes no statistics (a "dynamic tanh"): out = tanh(alpha * x) * gain + bias, with one scalar alpha.
 // Fused with the residual sum like the norms above: x = resid (+ a) (+ b), the two optional branches in the output's
 // type; the sum is written back to the float stream unless rows are selected.  Everything is elementwise, so the grid is
-// (pieces of a row, rows) and a thread takes four neighbouring features where the rows start on 16 bytes.
+// (pieces of a row, rows) and a thread takes eight neighbouring features where the rows start on 16 bytes.
 // `alpha` is read from device memory (it is a weight).
 // ---------------------------------------------------------------------------------------
 namespace {
@@ -459,34 +459,41 @@ add_dyt_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __re
     const int e0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (e0 >= hidden) return;
     const float al = *alpha;
-    float x[VEC];
-    if constexpr (VEC == 4) {
-        const float4 f = *reinterpret_cast<const float4*>(resid + src + e0);
-        x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
-    } else {
-        x[0] = resid[src + e0];
-    }
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        if (a) x[i] += ns_ld(a, src + e0 + i);
-        if (b) x[i] += ns_ld(b, src + e0 + i);
-    }
-    if (write_resid && (a || b)) {
-        if constexpr (VEC == 4) *reinterpret_cast<float4*>(resid + src + e0) = make_float4(x[0], x[1], x[2], x[3]);
-        else resid[src + e0] = x[0];
-    }
     T* o = out + (size_t)r * hidden + e0;
+    if constexpr (VEC == 8) {  // eight neighbouring features with 16-byte accesses
+        float x[8], t[8], g[8];
+        ld8(resid + src + e0, x);
+        if (a) {
+            ld8(a + src + e0, t);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) ns_st(o, i, fmaf(tanhf(al * x[i]), gain[e0 + i], bias ? bias[e0 + i] : 0.f));
+            for (int i = 0; i < 8; ++i) x[i] += t[i];
+        }
+        if (b) {
+            ld8(b + src + e0, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] += t[i];
+        }
+        if (write_resid && (a || b)) st8(resid + src + e0, x);
+        ld8(gain + e0, g);
+        if (bias) ld8(bias + e0, t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = fmaf(tanhf(al * x[i]), g[i], bias ? t[i] : 0.f);
+        st8(o, x);
+    } else {
+        float x = resid[src + e0];
+        if (a) x += ns_ld(a, src + e0);
+        if (b) x += ns_ld(b, src + e0);
+        if (write_resid && (a || b)) resid[src + e0] = x;
+        ns_st(o, 0, fmaf(tanhf(al * x), gain[e0], bias ? bias[e0] : 0.f));
+    }
 }
 
 template <typename T>
 int launch_add_dyt(float* resid, const void* a, const void* b, const float* gain, const float* bias, const float* alpha, void* out,
                    const int* rows, int n_rows, int hidden, int write_resid, cudaStream_t stream) {
-    const bool vec = hidden % 4 == 0 && ((uintptr_t)resid % 16 == 0);
-    if (n_rows > 65535 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_add_dyt: %d rows", n_rows);
-    const int per = vec ? 4 : 1;
-    const int threads = 256;
+    const bool vec = hidden % 8 == 0 && (((uintptr_t)resid | (uintptr_t)a | (uintptr_t)b | (uintptr_t)gain | (uintptr_t)bias | (uintptr_t)out) % 16 == 0);
+    const int per = vec ? 8 : 1;
+    const int threads = hidden / per >= 256 ? 256 : hidden / per > 64 ? 128 : 64;
     const unsigned bx = (unsigned)((hidden + threads * per - 1) / (threads * per));
     // the grid's y extent holds 65,535 rows: longer steps go in slices
     for (int r0 = 0; r0 < n_rows; r0 += 65535) {
@@ -496,7 +503,7 @@ int launch_add_dyt(float* resid, const void* a, const void* b, const float* gain
         const T* bs = b && !rows ? (const T*)b + (size_t)r0 * hidden : (const T*)b;
         T* os = (T*)out + (size_t)r0 * hidden;
         const int* rw = rows ? rows + r0 : nullptr;
-        if (vec) NS_LAUNCH((add_dyt_kernel<T, 4>), dim3(bx, nr), threads, 0, stream, rs, as, bs, gain, bias, alpha, os, rw, hidden, write_resid);
+        if (vec) NS_LAUNCH((add_dyt_kernel<T, 8>), dim3(bx, nr), threads, 0, stream, rs, as, bs, gain, bias, alpha, os, rw, hidden, write_resid);
         else NS_LAUNCH((add_dyt_kernel<T, 1>), dim3(bx, nr), threads, 0, stream, rs, as, bs, gain, bias, alpha, os, rw, hidden, write_resid);
     }
     NS_CHECK_LAUNCH("ns_add_dyt");

@@ -122,6 +122,140 @@ head_prepare_store_kernel(const T* __restrict__ proj, int ld_proj, T* __restrict
     }
 }
 
+// The same steps with 16-byte accesses, when heads, rotated parts, rows and caches allow it: a thread holds eight neighbouring
+// features of a head in registers, the d / 8 threads of a head are a group of `gs` lanes (a power of two, so that a warp holds whole
+// groups), sums over a head are exchanged within the group, and in the halves' pairing a thread gets its partner's features from
+// the lane rot_pairs / 8 away.  No shared memory; a block per token, every group takes heads in turn.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __restrict__ out, int ld_out,
+                              const int* __restrict__ positions, const int* __restrict__ token_req,
+                              const int* __restrict__ qo_indptr, const int* __restrict__ state_slot,
+                              const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
+                              float magnitude, int interleaved, int rot_pairs, const float* __restrict__ q_gain,
+                              const float* __restrict__ k_gain, int norm_mode, float eps, float temp_coef, float temp_every,
+                              const float* __restrict__ taps, int n_taps, const float* __restrict__ state, long long state_floats,
+                              T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d, int dv,
+                              int v_from_k, int write_kv, int gs) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int n = blockIdx.x;
+    const int req = token_req[n];
+    if (req < 0) return;
+    const int pos = positions[n];
+    const int C = nq * d + nkv * d + (v_from_k ? 0 : nkv * dv);
+    const int start = n_taps > 1 ? qo_indptr[req] : 0;
+    const int t = n - start;
+    const float* tail = n_taps > 1 ? state + (long long)state_slot[req] * state_floats : nullptr;
+    size_t slot = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)req * table_stride + pos / page_size];
+        slot = (size_t)page * nkv * page_size + (size_t)(pos % page_size);
+    }
+    const float fpos = (float)pos;
+    float temp = 1.f;
+    if (temp_every > 0.f) temp = 1.f + temp_coef * logf((float)floor((double)(pos + 1) / (double)temp_every) + 1.f);
+    const int units = nq + nkv + (v_from_k ? 0 : nkv);
+    const int total = units * gs;
+    const int lane = threadIdx.x & 31;
+    const int rp8 = rot_pairs / 8;  // halves' pairing: the partner chunk lies so many lanes away
+    for (int w0 = threadIdx.x - lane; w0 < total; w0 += blockDim.x) {  // the same trips for every lane of a warp
+        const int w = w0 + lane;
+        const int u = w / gs, c = w - u * gs;  // head unit and chunk of eight features
+        const bool is_q = u < nq, is_k = !is_q && u < nq + nkv, is_v = !is_q && !is_k;
+        const int hk = is_k ? u - nq : u - nq - nkv;
+        const int width = is_v ? dv : d;
+        const bool on = u < units && c * 8 < width;
+        const int col = (is_v ? (nq + nkv) * d + hk * dv : u * d) + c * 8;
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = 0.f;
+        if (on) {
+            if (taps) {
+                for (int j = 0; j < n_taps; ++j) {
+                    const int i2 = t - (n_taps - 1) + j;
+                    float in[8];
+                    if (i2 >= 0) ld8(proj + (size_t)(start + i2) * ld_proj + col, in);
+                    else ld8(tail + (size_t)(i2 + n_taps - 1) * C + col, in);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = fmaf(taps[(size_t)(col + i) * n_taps + j], in[i], x[i]);
+                }
+            } else {
+                ld8(proj + (size_t)n * ld_proj + col, x);
+            }
+            if (write_kv && (is_v || (is_k && v_from_k))) st8(v_cache + (slot + (size_t)hk * page_size) * dv + c * 8, x);
+        }
+        // (v units go through the exchanges below like the others and store nothing more)
+        const float* gain = is_q ? q_gain : k_gain;
+        const bool qk = on && !is_v;
+        if (norm_mode == 1) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+            for (int o = gs >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = rsqrtf(ss / (float)d + eps);
+            if (qk) {
+                float g[8];
+                if (gain) ld8(gain + c * 8, g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * (gain ? g[i] : 1.f);
+            }
+        }
+        if (rot_pairs > 0) {
+            if (interleaved) {
+                if (qk && c * 8 < 2 * rot_pairs) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float sn, cs;
+                        sincosf(fpos * inv_freq[c * 4 + i], &sn, &cs);
+                        sn *= magnitude; cs *= magnitude;
+                        const float a = x[2 * i], b = x[2 * i + 1];
+                        x[2 * i] = a * cs - b * sn;
+                        x[2 * i + 1] = b * cs + a * sn;
+                    }
+                }
+            } else {
+                const bool low = c < rp8, high = !low && c < 2 * rp8;
+                const int from = low ? lane + rp8 : lane - rp8;  // the partner's lane (unused outside the rotated part)
+                float y[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = __shfl_sync(0xffffffffu, x[i], (low || high) ? from : lane);
+                if (qk && (low || high)) {
+                    const int p0 = (low ? c : c - rp8) * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float sn, cs;
+                        sincosf(fpos * inv_freq[p0 + i], &sn, &cs);
+                        sn *= magnitude; cs *= magnitude;
+                        x[i] = low ? x[i] * cs - y[i] * sn : x[i] * cs + y[i] * sn;
+                    }
+                }
+            }
+        }
+        if (norm_mode == 2) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+            for (int o = gs >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = rsqrtf(ss / (float)d + eps);
+            if (qk) {
+                float g[8];
+                if (gain) ld8(gain + c * 8, g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * (gain ? g[i] : 1.f);
+            }
+        }
+        if (qk) {
+            if (is_q) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] *= temp;
+            }
+            st8(out + (size_t)n * ld_out + col, x);
+            if (is_k && write_kv) st8(k_cache + (slot + (size_t)hk * page_size) * d + c * 8, x);
+        }
+    }
+}
+
 }  // namespace
 
 NS_API int ns_head_prepare_store(const void* proj, int ld_proj, void* out, int ld_out, const int* positions, const int* token_req,
@@ -142,6 +276,34 @@ NS_API int ns_head_prepare_store(const void* proj, int ld_proj, void* out, int l
     if (n_taps > 1 && (!state || !qo_indptr || !state_slot)) NS_FAIL(NS_ERR_ARGUMENT, "ns_head_prepare_store: a convolution over several tokens needs a state");
     if (n_taps > 1 && proj == out) NS_FAIL(NS_ERR_ARGUMENT, "ns_head_prepare_store: a convolution cannot run in place");
     const int dmax = d > dv ? d : dv;
+    // 16-byte accesses: heads, the rotated part (in the halves' pairing also each half), rows and caches in multiples of eight features
+    int gs = 1;
+    while (gs * 8 < dmax) gs *= 2;
+    const bool vec = d % 8 == 0 && dv % 8 == 0 && gs <= 32 && ld_proj % 8 == 0 && ld_out % 8 == 0 && (2 * rot_pairs) % 8 == 0 &&
+                     (interleaved || rot_pairs % 8 == 0) &&
+                     (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)state |
+                       (write_kv ? ((uintptr_t)k_cache | (uintptr_t)v_cache) : 0)) % 16 == 0) &&
+                     (n_taps <= 1 || state_floats % 4 == 0);
+    if (vec) {
+        const int units = nq + nkv + (v_from_k ? 0 : nkv);
+        const int lanes = units * gs;
+        const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
+        if (dtype == NS_F32)
+            NS_LAUNCH((head_prepare_store_vec_kernel<float>), n_tokens, threads, 0, stream, (const float*)proj, ld_proj, (float*)out,
+                      ld_out, positions, token_req, qo_indptr, state_slot, block_table, table_stride, inv_freq, magnitude, interleaved,
+                      rot_pairs, q_gain, k_gain, norm_mode, eps, temp_coef, temp_every, taps, n_taps, state, state_floats,
+                      (float*)k_cache, (float*)v_cache, page_size, nq, nkv, d, dv, v_from_k, write_kv, gs);
+        else if (dtype == NS_BF16)
+            NS_LAUNCH((head_prepare_store_vec_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, (const __nv_bfloat16*)proj,
+                      ld_proj, (__nv_bfloat16*)out, ld_out, positions, token_req, qo_indptr, state_slot, block_table, table_stride,
+                      inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, norm_mode, eps, temp_coef, temp_every, taps, n_taps,
+                      state, state_floats, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, dv, v_from_k,
+                      write_kv, gs);
+        else
+            NS_FAIL(NS_ERR_ARGUMENT, "ns_head_prepare_store: unknown dtype %d", dtype);
+        NS_CHECK_LAUNCH("ns_head_prepare_store");
+        return NS_OK;
+    }
     const size_t smem = (size_t)kPrepWarps * dmax * sizeof(float);
     if (smem > 48 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_head_prepare_store: heads of %d features", dmax);
     if (dtype == NS_F32)

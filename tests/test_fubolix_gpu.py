@@ -284,26 +284,28 @@ def test_attention_kernels_with_a_sink_and_gated_heads(d, dv, H, G, window, keep
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["float32", "bfloat16"])
-def test_head_preparation_kernel_alone(dtype):
+@pytest.mark.parametrize("nq,nkv,d,dv_other,rot_dims", [(3, 2, 12, 8, 8), (3, 2, 16, 8, 16), (5, 1, 48, 24, 32), (2, 2, 64, 64, 16)],
+                         ids=["one feature at a time", "eight at a time", "heads of 48", "heads of 64"])
+def test_head_preparation_kernel_alone(nq, nkv, d, dv_other, rot_dims, dtype):
     """The convolution with its tail carried from step to step, the head norms before and after the rotation, both pairings, the
     query temperature, keys that double as values, and what lands in the cache: two requests in portions against the plain
     functions over the whole sequences."""
     from nanospec_b200 import ops
 
     g = torch.Generator().manual_seed(11)
-    nq, nkv, d, page = 3, 2, 12, 4
+    page = 4
     lengths, cuts = [19, 11], [[5, 1, 2, 11], [2, 6, 1, 2]]
     for case in ("conv", "norm after, values from keys", "norm before, temperature", "one tap"):
-        dv = d if case.startswith("norm after") else 8
+        dv = d if case.startswith("norm after") else dv_other
         v_from_k = case.startswith("norm after")
         cols = (nq + nkv) * d + (0 if v_from_k else nkv * dv)
         taps_n = {"conv": 4, "one tap": 1}.get(case, 0)
         taps = (torch.randn(cols, taps_n, generator=g) * 0.6).to(BF16).float() if taps_n else None
-        rot = {"dims": 8, "base": 300.0, "scaling": YARN}
+        rot = {"dims": rot_dims, "base": 300.0, "scaling": YARN}
         layout = "half" if case == "conv" else "interleaved"
         f, mag = plain.yarn_frequencies(rot)
         gains = (1.0 + 0.3 * torch.randn(2, d, generator=g)) if case.startswith("norm before") else None
-        seqs = [torch.randn(n, cols + 5, generator=g).to(dtype).float() for n in lengths]  # the rows are wider than [q | k | v]
+        seqs = [torch.randn(n, cols + 8, generator=g).to(dtype).float() for n in lengths]  # the rows are wider than [q | k | v]
         want = []
         for x in seqs:
             u = x[:, :cols].double()
