@@ -5,7 +5,8 @@
 //
 // A row of the projection is [q: nq*d | k: nkv*d | v: nkv*dv]; with `v_from_k` there is no v part and the values are
 // the keys as projected (after the convolution, before norm and rotation; dv = d).  In order, per head:
-//   1. convolution (`taps` given):  y_t[c] = sum_j taps[c, j] * x_(t - n_taps + 1 + j)[c]; inputs before this step's
+//   1. convolution (`taps` given, [n_taps, C]: one row per tap, so that neighbouring channels' weights lie side by side):
+//      y_t[c] = sum_j taps[j, c] * x_(t - n_taps + 1 + j)[c]; inputs before this step's
 //      first token of the request come from the request's tail [(n_taps - 1), C] in its state slot, which is zero at a
 //      sequence's start.  `ns_conv_tail` (recurrent.cu) moves the tail on afterwards.
 //   2. values: stored (v heads, or the k heads' features at this point when v_from_k).
@@ -71,7 +72,7 @@ head_prepare_store_kernel(const T* __restrict__ proj, int ld_proj, T* __restrict
                 for (int j = 0; j < n_taps; ++j) {
                     const int i = t - (n_taps - 1) + j;
                     const float in = i >= 0 ? ns_ld(proj, (size_t)(start + i) * ld_proj + c) : tail[(size_t)(i + n_taps - 1) * C + c];
-                    acc = fmaf(taps[(size_t)c * n_taps + j], in, acc);
+                    acc = fmaf(taps[(size_t)j * C + c], in, acc);
                 }
             } else {
                 acc = ns_ld(proj, (size_t)n * ld_proj + c);
@@ -174,11 +175,12 @@ head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __rest
             if (taps) {
                 for (int j = 0; j < n_taps; ++j) {
                     const int i2 = t - (n_taps - 1) + j;
-                    float in[8];
+                    float in[8], tw[8];
                     if (i2 >= 0) ld8(proj + (size_t)(start + i2) * ld_proj + col, in);
                     else ld8(tail + (size_t)(i2 + n_taps - 1) * C + col, in);
+                    ld8(taps + (size_t)j * C + col, tw);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) x[i] = fmaf(taps[(size_t)(col + i) * n_taps + j], in[i], x[i]);
+                    for (int i = 0; i < 8; ++i) x[i] = fmaf(tw[i], in[i], x[i]);
                 }
             } else {
                 ld8(proj + (size_t)n * ld_proj + col, x);
@@ -281,7 +283,7 @@ NS_API int ns_head_prepare_store(const void* proj, int ld_proj, void* out, int l
     while (gs * 8 < dmax) gs *= 2;
     const bool vec = d % 8 == 0 && dv % 8 == 0 && gs <= 32 && ld_proj % 8 == 0 && ld_out % 8 == 0 && (2 * rot_pairs) % 8 == 0 &&
                      (interleaved || rot_pairs % 8 == 0) &&
-                     (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)state |
+                     (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)state | (uintptr_t)taps |
                        (write_kv ? ((uintptr_t)k_cache | (uintptr_t)v_cache) : 0)) % 16 == 0) &&
                      (n_taps <= 1 || state_floats % 4 == 0);
     if (vec) {

@@ -1218,8 +1218,9 @@ def head_prepare_store(proj: torch.Tensor, out: torch.Tensor, ctx, lane, nq: int
                        eps: float = 0.0, q_temp: tuple[float, float] | None = None, taps: torch.Tensor | None = None,
                        v_from_k: bool = False, write_kv: bool = True) -> None:
     """Rows [q: nq*head_dim | k: nkv*head_dim | v: nkv*v_dim] of `proj` (no v part when `v_from_k`: the values are the keys as
-    projected), head by head (csrc/head_prepare.cu): a causal convolution over time per channel (`taps` [channels, n] float32; the
-    last n - 1 inputs of every request live in `lane.state` and move on by this step's tokens), an RMS norm per head (`norm`
+    projected), head by head (csrc/head_prepare.cu): a causal convolution over time per channel (`taps` [n, channels] float32, one row
+    per tap, the last row the current token's; the last n - 1 inputs of every request live in `lane.state` and move on by this
+    step's tokens), an RMS norm per head (`norm`
     "before" or "after" the rotation; gains [head_dim] float32 shared by the heads, or none), the rotation of the first
     2 * len(inv_freq) features (pairs (2i, 2i+1) when `interleaved`, (i, i + len) otherwise; cos and sin times `magnitude`), the
     queries times 1 + coef * ln(floor((position + 1) / every) + 1) for `q_temp` = (coef, every).  q and k go to `out` (which may be
@@ -1237,10 +1238,10 @@ def head_prepare_store(proj: torch.Tensor, out: torch.Tensor, ctx, lane, nq: int
     n_taps = 1
     state = None
     if taps is not None:
-        n_taps = int(taps.shape[1])
+        n_taps = int(taps.shape[0])
         state = lane.state
-        if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.shape[0] != cols:
-            raise KernelError("head_prepare_store: float32 taps, one row per channel of [q | k | v]")
+        if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.dim() != 2 or taps.shape[1] != cols:
+            raise KernelError("head_prepare_store: float32 taps, one row per tap over the channels of [q | k | v]")
         if n_taps > 1 and (state is None or state.dtype != torch.float32 or not state.is_contiguous()
                            or state[0].numel() < (n_taps - 1) * cols):
             raise KernelError("head_prepare_store: the convolution's last inputs need a float32 state of (taps - 1) * channels per slot")

@@ -164,7 +164,8 @@ class GQAAttention(Part):
         elif self.sink_kind == "zero":
             self.sink = torch.zeros(self.heads, dtype=torch.float32, device=self.w_o.device)
         if self.taps:
-            self.conv_taps = torch.cat([tensors[n[k + "_conv"]] for k in kinds], dim=0).contiguous()
+            # [taps, channels]: a tap's weights of neighbouring channels lie side by side, as the kernel reads them
+            self.conv_taps = torch.cat([tensors[n[k + "_conv"]] for k in kinds], dim=0).t().contiguous()
         if self.qk_norm is not None:
             self.q_gain = tensors[n["q_norm"]].contiguous()
             self.k_gain = tensors[n["k_norm"]].contiguous() if self.own_kv else None

@@ -342,7 +342,7 @@ def test_head_preparation_kernel_alone(nq, nkv, d, dv_other, rot_dims, dtype):
             ops.head_prepare_store(rows, out, ctx, lane, nq, nkv, d, dv, inv_freq=f.float().cuda(), magnitude=mag, interleaved=layout == "interleaved",
                                    norm="after" if v_from_k else "before" if gains is not None else None,
                                    q_gain=gains[0].cuda() if gains is not None else None, k_gain=gains[1].cuda() if gains is not None else None,
-                                   eps=1e-5, q_temp=(0.4, 3.0) if gains is not None else None, taps=taps.cuda() if taps is not None else None,
+                                   eps=1e-5, q_temp=(0.4, 3.0) if gains is not None else None, taps=taps.t().contiguous().cuda() if taps is not None else None,
                                    v_from_k=v_from_k)
             o = out.float().cpu()
             row = 0
