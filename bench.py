@@ -960,7 +960,7 @@ def fubolix_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, p
         out["ns_attention_prefill_kept"] = 4.0 * H * d * (n_win * pairs_w + n_all * pairs_all) / tc
     else:
         out["ns_attention_decode_kept"] = 4.0 * (n_win * pairs_w + n_all * pairs_all) * nkv * d / bw
-    out["ns_activation"] = L * 4.0 * N * sz["ff"] / bw
+    out["ns_activation"] = out["ns_activation_rows"] = L * 4.0 * N * sz["ff"] / bw  # (rows of a wider buffer when the block packs its products)
     out["ns_residual_add"] = 10.0 * N * W / bw
     out["ns_embed_streams"] = 6.0 * N * W / bw
     return out

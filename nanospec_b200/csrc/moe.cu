@@ -300,6 +300,28 @@ __global__ void activation_vec_kernel(const T* __restrict__ x, T* __restrict__ o
     st8(out + i * 8, v);
 }
 
+// rows of `cols` features with strides of their own (column ranges of wider buffers); VEC = 8 needs both rows on 16 bytes
+template <typename T, int VEC>
+__global__ void activation_rows_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ out, long long ldo, int cols, int kind,
+                                       size_t total) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int per_row = cols / VEC;
+    const size_t row = i / per_row;
+    const int c = (int)(i - row * per_row) * VEC;
+    if constexpr (VEC == 8) {
+        float v[8];
+        ld8(x + row * ldx + c, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = act_value(v[k], kind);
+        st8(out + row * ldo + c, v);
+    } else {
+        ns_st(out, row * ldo + c, act_value(ns_ld(x, row * ldx + c), kind));
+    }
+}
+
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, int kind, size_t total) {
     ns_pdl_launch_dependents();
@@ -413,6 +435,27 @@ NS_API int ns_moe_expert_rows(const void* x, const int* ids, const float* weight
     else NS_FAIL(NS_ERR_ARGUMENT, "ns_moe_expert_rows: unknown dtype %d", dtype);
 #undef NS_MOE_ROWS
     NS_CHECK_LAUNCH("ns_moe_expert_rows");
+    return NS_OK;
+}
+
+// the same over rows that lie in wider buffers: x[r * ldx + c] -> out[r * ldo + c], c < cols
+NS_API int ns_activation_rows(const void* x, long long ldx, void* out, long long ldo, int n_rows, int cols, int kind, int dtype,
+                              cudaStream_t stream) {
+    if (n_rows <= 0 || cols <= 0) return NS_OK;
+    if (kind < 0 || kind > 3) NS_FAIL(NS_ERR_ARGUMENT, "ns_activation_rows: unknown kind %d", kind);
+    if (dtype != NS_F32 && dtype != NS_BF16) NS_FAIL(NS_ERR_ARGUMENT, "ns_activation_rows: unknown dtype %d", dtype);
+    const size_t esz = dtype == NS_F32 ? 4 : 2;
+    const bool vec = cols % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) % 16 == 0) && (ldx * esz) % 16 == 0 && (ldo * esz) % 16 == 0;
+    const size_t total = (size_t)n_rows * (vec ? cols / 8 : cols);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == NS_F32) {
+        if (vec) NS_LAUNCH((activation_rows_kernel<float, 8>), blocks, 256, 0, stream, (const float*)x, ldx, (float*)out, ldo, cols, kind, total);
+        else NS_LAUNCH((activation_rows_kernel<float, 1>), blocks, 256, 0, stream, (const float*)x, ldx, (float*)out, ldo, cols, kind, total);
+    } else {
+        if (vec) NS_LAUNCH((activation_rows_kernel<__nv_bfloat16, 8>), blocks, 256, 0, stream, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, cols, kind, total);
+        else NS_LAUNCH((activation_rows_kernel<__nv_bfloat16, 1>), blocks, 256, 0, stream, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, cols, kind, total);
+    }
+    NS_CHECK_LAUNCH("ns_activation_rows");
     return NS_OK;
 }
 

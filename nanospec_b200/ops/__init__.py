@@ -1007,8 +1007,14 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
     _cuda(x, out)
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation: unknown kind {kind!r} (known: {', '.join(ACTIVATIONS)})")
+    if x.shape == out.shape and x.dtype == out.dtype and x.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1 \
+            and not (x.is_contiguous() and out.is_contiguous()):
+        # column ranges of wider buffers: rows with strides of their own
+        lib.call("ns_activation_rows", x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], ACTIVATIONS[kind],
+                 dtype_code(x.dtype), _stream())
+        return out
     if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
-        raise KernelError("activation: contiguous operands of one shape and dtype")
+        raise KernelError("activation: operands of one shape and dtype, contiguous or rows with unit inner stride")
     lib.call("ns_activation", x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], dtype_code(x.dtype), _stream())
     return out
 

@@ -75,6 +75,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_expert_rows": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "ns_activation": [_P, _P, _L, _I, _I, _P],
+    "ns_activation_rows": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
     "ns_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
     "ns_token_gate": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _I, _I, _P],
     "ns_sigmoid_mul": [_P, _L, _P, _L, _I, _I, _I, _P],

@@ -233,13 +233,41 @@ class GQAAttention(Part):
         return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)
 
     def _forward_per_head(self, x, ctx: StepContext, lane: LaneView, writes: bool):
-        """Projection, `ops.head_prepare_store` (convolution, head norms, rotation, query temperature, cache write), attention with the
-        sink and the heads' gates in its epilogue, output projection."""
+        """Projection, the per-head steps and the attention (`forward_projected`), output projection."""
+        proj = ops.linear(x, self.w_qkv, ctx.buffer("qkv_in" if self.taps > 1 else "qkv", self.w_qkv.shape[0]))
+        attn = ctx.buffer("attn_out", self.o_in)
+        self.forward_projected(proj, ctx, lane, writes, attn)
+        return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden))
+
+    # ---- optional: an arrangement that runs this mixer's projections inside larger products of its own ---------------------
+    # (`packs_projections`: the mixer offers `input_weight` [columns, hidden] and `output_weight` [hidden, heads * v_dim], takes views
+    # of the arrangement's packed matrices in their place (`adopt`), and runs everything between the two products on rows that the
+    # arrangement hands it: `forward_projected`)
+    @property
+    def packs_projections(self) -> bool:
+        return self.per_head
+
+    @property
+    def input_weight(self) -> torch.Tensor:
+        return self.w_qkv
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.w_o
+
+    def adopt(self, w_in: torch.Tensor, w_out: torch.Tensor) -> None:
+        if w_in.shape != self.w_qkv.shape or w_out.shape != self.w_o.shape:
+            raise ValueError("adopt: views of the projections' own shapes are needed")
+        self.w_qkv, self.w_o = w_in, w_out
+
+    def forward_projected(self, proj: torch.Tensor, ctx: StepContext, lane: LaneView, writes: bool, attn: torch.Tensor) -> None:
+        """`proj` [N, >= columns of the packed projection] (rows may lie in a wider buffer): `ops.head_prepare_store` (convolution,
+        head norms, rotation, query temperature, cache write), then attention with the sink and the heads' gates in its epilogue into
+        `attn` [N, heads * v_dim] (likewise)."""
         if self.taps > 1 and not writes:
             raise ValueError("an attention mixer with a convolution owns its state: its lane cannot be shared")
-        cols = self.w_qkv.shape[0]
-        proj = ops.linear(x, self.w_qkv, ctx.buffer("qkv_in" if self.taps > 1 else "qkv", cols))
-        qkv = ctx.buffer("qkv", cols) if self.taps > 1 else proj  # a convolution reads its neighbours' rows: not in place
+        # a convolution reads its neighbours' rows: not in place
+        qkv = ctx.buffer("qkv", self.w_qkv.shape[0]) if self.taps > 1 else proj
         pos, hn = self.position, self.head_norm
         rotates = pos is not None and pos.dims > 0
         ops.head_prepare_store(
@@ -250,7 +278,5 @@ class GQAAttention(Part):
             q_temp=(float(self.q_temp["coef"]), float(self.q_temp["every"])) if self.q_temp else None,
             taps=self.conv_taps, v_from_k=self.v_from_k, write_kv=writes)
         gate = proj[:, self.channels: self.channels + self.heads] if self.head_gate else None
-        attn = ctx.buffer("attn_out", self.o_in)
         ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window, self.keep_first,
                       self.v_dim, self.wide_weights, self.chunk, self.softcap, sink=self.sink, gate=gate)
-        return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden))

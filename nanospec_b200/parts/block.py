@@ -30,6 +30,10 @@ stream's copy in the compute type for the next sublayer; the block hands that co
 added by a kernel of its own when the norm that comes next takes two pending branches (`takes_branches`, as the "dyt" norm does):
 the block leaves the pair pending and that norm's kernel sums stream, mixer branch and feed-forward branch in float32.  Otherwise the
 mixer's branch joins the stream through `ops.residual_add` and the feed-forward's stays pending as a tensor.
+When both sublayers offer their projections (`packs_projections`) the block runs TWO products a layer instead of four: one packed
+input projection [mixer's columns | feed-forward's] of h, and one output projection of the concatenated [heads' outputs |
+activations] by [W_o | W_down], whose float32 accumulator holds mixer(h) + feed_forward(h) before it is rounded once; the sublayers
+keep views of the packed matrices in place of their own (`adopt`), so weights are held once and replaced in place.
 """
 
 from __future__ import annotations
@@ -174,12 +178,16 @@ class OutNormBlock:
 class ParallelBlock:
     slots = ("norm_mixer", "mixer", "feed_forward")
     takes_follow = True
+    PACK = True  # False: the sublayers run their own products (measurements and tests of that path)
 
     def __init__(self, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
         self.layer = layer
         self.mixer = build_part("mixer", layer.mixer, dtype, device)
         self.norm_mixer = build_part("norm", layer.norm, dtype, device)
         self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device) if layer.feed_forward is not None else None
+        self.w_in: torch.Tensor | None = None   # [mixer's columns + feed-forward's, hidden] once packed
+        self.w_out: torch.Tensor | None = None  # [hidden, heads' outputs + activations]
+        self._packed: bool | None = None        # decided when the weights are bound
 
     def parts(self) -> dict:
         return {s: getattr(self, s) for s in self.slots if getattr(self, s) is not None}
@@ -196,10 +204,38 @@ class ParallelBlock:
             return pending[1]
         return pending
 
+    def _pack(self) -> bool:
+        """Packs the sublayers' projections once.  Widths in multiples of eight only: rows of the packed buffers then start on 16 bytes
+        in bfloat16, which the sublayers' kernels ask of their operands."""
+        m, f = self.mixer, self.feed_forward
+        if not (self.PACK and f is not None and getattr(m, "packs_projections", False) and getattr(f, "packs_projections", False)):
+            return False
+        wi_m, wi_f, wo_m, wo_f = m.input_weight, f.input_weight, m.output_weight, f.output_weight
+        if any(w is None for w in (wi_m, wi_f, wo_m, wo_f)) or any(w.shape[0] % 8 or w.shape[1] % 8 for w in (wi_m, wi_f, wo_m, wo_f)):
+            return False
+        self.w_in = torch.cat([wi_m, wi_f], dim=0).contiguous()
+        self.w_out = torch.cat([wo_m, wo_f], dim=1).contiguous()
+        m.adopt(self.w_in[: wi_m.shape[0]], self.w_out[:, : wo_m.shape[1]])
+        f.adopt(self.w_in[wi_m.shape[0]:], self.w_out[:, wo_m.shape[1]:])
+        return True
+
+    def after_bind(self) -> None:
+        """Called by the model once every part has its weights."""
+        self._packed = self._pack()
+
     def forward(self, resid: torch.Tensor, pending, ctx: StepContext, lane: LaneView, writes: bool = True, follow=None):
+        if self._packed is None:  # parts bound by hand: pack now, unless a graph is being captured (no allocation then)
+            self._packed = False if torch.cuda.is_current_stream_capturing() else self._pack()
         if isinstance(pending, tuple) and not self.takes_pair():
             pending = self._settle(resid, pending)
         h = self.norm_mixer.add_norm(resid, pending, ctx)
+        if self._packed:
+            cm, om = self.mixer.input_weight.shape[0], self.mixer.output_weight.shape[1]
+            proj = ops.linear(h, self.w_in, ctx.buffer("par_in", self.w_in.shape[0]))
+            mid = ctx.buffer("par_mid", self.w_out.shape[1])
+            self.mixer.forward_projected(proj[:, :cm], ctx, lane, writes, mid[:, :om])
+            self.feed_forward.forward_projected(proj[:, cm:], ctx, mid[:, om:])
+            return resid, ops.linear(mid, self.w_out, ctx.buffer("branch", resid.shape[1]))
         a = self.mixer.forward(h, ctx, lane, writes)
         if self.feed_forward is None:
             return resid, a

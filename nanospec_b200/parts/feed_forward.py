@@ -95,3 +95,23 @@ class DenseAct(Part):
         u = ops.linear(x, self.w_up, ctx.buffer("ffn_up", self.inter))
         a = ops.activation(u, ctx.buffer("ffn_act", self.inter), self.activation)
         return ops.linear(a, self.w_down, ctx.buffer(out_name, self.hidden))
+
+    # ---- optional: an arrangement that runs the two products inside larger ones of its own (see `GQAAttention.packs_projections`)
+    packs_projections = True
+
+    @property
+    def input_weight(self) -> torch.Tensor:
+        return self.w_up
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.w_down
+
+    def adopt(self, w_in: torch.Tensor, w_out: torch.Tensor) -> None:
+        if w_in.shape != self.w_up.shape or w_out.shape != self.w_down.shape:
+            raise ValueError("adopt: views of the projections' own shapes are needed")
+        self.w_up, self.w_down = w_in, w_out
+
+    def forward_projected(self, u: torch.Tensor, ctx: StepContext, act: torch.Tensor) -> None:
+        """`u` [N, intermediate] (rows may lie in a wider buffer): the activation into `act` (likewise)."""
+        ops.activation(u, act, self.activation)

@@ -52,6 +52,10 @@ class DecoderModel:
         """`weights`: full name -> tensor on the device, already cast (see weights/loader.py)."""
         for prefix, part in self._named_parts():
             part.bind({name: weights[prefix + name] for name in part.weight_specs()})
+        for block in self.blocks:  # an arrangement may lay its parts' tensors out anew once all of them are bound
+            after = getattr(block, "after_bind", None)
+            if callable(after):
+                after()
         self.bound = True
 
     # ---- cache needs, one entry per lane ------------------------------------------------

@@ -399,6 +399,28 @@ def test_each_mechanism(name, dtype, tmp_path):
         close(run_cut(runner, 0, ids, cuts), want, dtype, f"{name}, portions {cuts or 'of one'}", noise)
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["float32", "bfloat16"])
+def test_sublayers_with_products_of_their_own(dtype, tmp_path):
+    """The arrangement with its packing switched off: four products a layer, the pair of branches pending for the next norm."""
+    from nanospec_b200.parts.block import ParallelBlock
+
+    cfg = config([windowed(dense(16), heads=4, kv_heads=2, dim=16), convolved(dense(32), dim=16, vdim=8), tempered(dense(24), dim=16, vdim=16)])
+    ids = tokens(37, cfg["vocab"], 5)
+    ParallelBlock.PACK = False
+    try:
+        runner, w = make(tmp_path, cfg, seed=77, dtype=dtype)
+    finally:
+        ParallelBlock.PACK = True
+    assert all(b.w_in is None for b in runner.model.blocks)
+    packed, _ = make(tmp_path / "p", cfg, seed=77, dtype=dtype, weights=w)
+    assert all(b.w_in is not None for b in packed.model.blocks)
+    want = plain.forward(cfg, w, ids)
+    noise = rounding(cfg, w, ids, want)
+    for cuts in ([37], [], [2, 3, 2, 11, 5, 2]):
+        close(run_cut(runner, 0, ids, cuts), want, dtype, f"own products, portions {cuts or 'of one'}", noise)
+        close(run_cut(packed, 0, ids, cuts), want, dtype, f"packed products, portions {cuts or 'of one'}", noise)
+
+
 def test_layers_one_by_one(tmp_path):
     """The stream after every layer, in float32, against the plain statement's."""
     from nanospec_b200.engine.step import StepEntry
