@@ -905,7 +905,7 @@ FUBOLIX_SIZES = {
     "w2048": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, layers=8),
     "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, layers=4),
 }
-FUBOLIX_CONV, FUBOLIX_TEMP_EVERY = 4, 64
+FUBOLIX_CONV, FUBOLIX_TEMP_EVERY = 4, 128
 
 
 def fubolix_config(sz: dict) -> dict:
@@ -916,7 +916,7 @@ def fubolix_config(sz: dict) -> dict:
     windowed = {"type": "attention", "mlp": mlp, "mixer": {**base, "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
                                                             "rot": {"dims": d // 2, "base": 1000000.0, "scaling": yarn}}}
     convolved = {"type": "attention_3", "mlp": mlp, "mixer": {**base, "conv": FUBOLIX_CONV, "rot": {"dims": d, "base": 1000000.0, "scaling": yarn}}}
-    tempered = {"type": "attention_2", "mlp": mlp, "mixer": {**base, "q_temp": {"coef": 0.3, "every": FUBOLIX_TEMP_EVERY}}}
+    tempered = {"type": "attention_2", "mlp": mlp, "mixer": {**base, "q_temp": {"coef": 0.25, "every": FUBOLIX_TEMP_EVERY}}}
     pattern = [windowed, convolved, windowed, tempered]
     return {"architecture": "Fubolix", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
             "layers": [pattern[i % 4] for i in range(sz["layers"])]}

@@ -126,7 +126,8 @@ head_prepare_store_kernel(const T* __restrict__ proj, int ld_proj, T* __restrict
 // The same steps with 16-byte accesses, when heads, rotated parts, rows and caches allow it: a thread holds eight neighbouring
 // features of a head in registers, the d / 8 threads of a head are a group of `gs` lanes (a power of two, so that a warp holds whole
 // groups), sums over a head are exchanged within the group, and in the halves' pairing a thread gets its partner's features from
-// the lane rot_pairs / 8 away.  No shared memory; a block per token, every group takes heads in turn.
+// the lane rot_pairs / 8 away.  The token's cosines and sines are computed once, into shared memory, for all of its heads; a block
+// per token, every group takes heads in turn.
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __restrict__ out, int ld_out,
@@ -156,6 +157,15 @@ head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __rest
     const float fpos = (float)pos;
     float temp = 1.f;
     if (temp_every > 0.f) temp = 1.f + temp_coef * logf((float)floor((double)(pos + 1) / (double)temp_every) + 1.f);
+    // the token's cosines and sines, once for all heads: [pair][cos, sin], already times the magnitude
+    extern __shared__ float cs_sn[];
+    for (int p = threadIdx.x; p < rot_pairs; p += blockDim.x) {
+        float sn, cs;
+        sincosf(fpos * inv_freq[p], &sn, &cs);
+        cs_sn[2 * p] = cs * magnitude;
+        cs_sn[2 * p + 1] = sn * magnitude;
+    }
+    __syncthreads();
     const int units = nq + nkv + (v_from_k ? 0 : nkv);
     const int total = units * gs;
     const int lane = threadIdx.x & 31;
@@ -208,9 +218,7 @@ head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __rest
                 if (qk && c * 8 < 2 * rot_pairs) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        float sn, cs;
-                        sincosf(fpos * inv_freq[c * 4 + i], &sn, &cs);
-                        sn *= magnitude; cs *= magnitude;
+                        const float cs = cs_sn[2 * (c * 4 + i)], sn = cs_sn[2 * (c * 4 + i) + 1];
                         const float a = x[2 * i], b = x[2 * i + 1];
                         x[2 * i] = a * cs - b * sn;
                         x[2 * i + 1] = b * cs + a * sn;
@@ -226,9 +234,7 @@ head_prepare_store_vec_kernel(const T* __restrict__ proj, int ld_proj, T* __rest
                     const int p0 = (low ? c : c - rp8) * 8;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        float sn, cs;
-                        sincosf(fpos * inv_freq[p0 + i], &sn, &cs);
-                        sn *= magnitude; cs *= magnitude;
+                        const float cs = cs_sn[2 * (p0 + i)], sn = cs_sn[2 * (p0 + i) + 1];
                         x[i] = low ? x[i] * cs - y[i] * sn : x[i] * cs + y[i] * sn;
                     }
                 }
@@ -290,13 +296,14 @@ NS_API int ns_head_prepare_store(const void* proj, int ld_proj, void* out, int l
         const int units = nq + nkv + (v_from_k ? 0 : nkv);
         const int lanes = units * gs;
         const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
+        const size_t rot_smem = (size_t)2 * rot_pairs * sizeof(float);
         if (dtype == NS_F32)
-            NS_LAUNCH((head_prepare_store_vec_kernel<float>), n_tokens, threads, 0, stream, (const float*)proj, ld_proj, (float*)out,
+            NS_LAUNCH((head_prepare_store_vec_kernel<float>), n_tokens, threads, rot_smem, stream, (const float*)proj, ld_proj, (float*)out,
                       ld_out, positions, token_req, qo_indptr, state_slot, block_table, table_stride, inv_freq, magnitude, interleaved,
                       rot_pairs, q_gain, k_gain, norm_mode, eps, temp_coef, temp_every, taps, n_taps, state, state_floats,
                       (float*)k_cache, (float*)v_cache, page_size, nq, nkv, d, dv, v_from_k, write_kv, gs);
         else if (dtype == NS_BF16)
-            NS_LAUNCH((head_prepare_store_vec_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, (const __nv_bfloat16*)proj,
+            NS_LAUNCH((head_prepare_store_vec_kernel<__nv_bfloat16>), n_tokens, threads, rot_smem, stream, (const __nv_bfloat16*)proj,
                       ld_proj, (__nv_bfloat16*)out, ld_out, positions, token_req, qo_indptr, state_slot, block_table, table_stride,
                       inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, norm_mode, eps, temp_coef, temp_every, taps, n_taps,
                       state, state_floats, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, dv, v_from_k,
