@@ -59,6 +59,10 @@ struct GemmEpilogue {
     __nv_bfloat16* sink_x;        // [tokens, sink_ld]
     float* sink_partials;         // [tokens, feature tiles * splits]
     int sink_ld;
+    // ... or, with sink_alpha given, a norm that takes no statistics follows: sink_x = bf16(tanh(alpha * resid) * gain + bias),
+    // complete as it is (no partials, and the product that reads it applies no scale)
+    const float* sink_bias;       // [features] or null
+    const float* sink_alpha;      // one float in device memory; null: the RMS form above
     // rope: the product is an attention layer's packed [q | k | v] projection.  q and k are rotated by the
     // token's position (pairs (j, j + head_dim / 2)); q goes to `out`, k and v to the token's slot of the cache
     // [page, kv head, offset, head_dim].  Tiles of 128 features hold whole heads (head_dim 32, 64 or 128).
@@ -123,6 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                int* __restrict__ error_flag) {
     const int gated = ep.gated;
     const bool sink = ep.sink_resid != nullptr;
+    const bool sink_tanh = ep.sink_alpha != nullptr;
     const bool rope = ep.rope_positions != nullptr;
     // per-token scale (scale mode) and squares of the finished residual (sink mode); both modes are
     // offered for tiles of up to 64 tokens
@@ -453,9 +458,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (kNorm && sink) {
                     res.x += acc.x; res.y += acc.y; res.z += acc.z; res.w += acc.w;
                     *reinterpret_cast<float4*>(ep.sink_resid + so) = res;
-                    store_out4(ep.sink_x + so, make_float4(res.x * gain[0], res.y * gain[1], res.z * gain[2], res.w * gain[3]));
-                    float* sq = sq_s + j * (BM + 1) + (i - i0);
-                    sq[0] = res.x * res.x; sq[1] = res.y * res.y; sq[2] = res.z * res.z; sq[3] = res.w * res.w;
+                    if (sink_tanh) {
+                        const float al = __ldg(ep.sink_alpha);
+                        float b[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (ep.sink_bias) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) b[c] = __ldg(ep.sink_bias + n0 + i + c);
+                        }
+                        store_out4(ep.sink_x + so, make_float4(fmaf(tanhf(al * res.x), gain[0], b[0]), fmaf(tanhf(al * res.y), gain[1], b[1]),
+                                                               fmaf(tanhf(al * res.z), gain[2], b[2]), fmaf(tanhf(al * res.w), gain[3], b[3])));
+                    } else {
+                        store_out4(ep.sink_x + so, make_float4(res.x * gain[0], res.y * gain[1], res.z * gain[2], res.w * gain[3]));
+                        float* sq = sq_s + j * (BM + 1) + (i - i0);
+                        sq[0] = res.x * res.x; sq[1] = res.y * res.y; sq[2] = res.z * res.z; sq[3] = res.w * res.w;
+                    }
                 } else {
                     OutT* dst = out + (size_t)(tok0 + j) * ldo + n0 + i;
                     if (n0 + i + 3 < N_feat) {
@@ -467,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                 }
             }
-            if (kNorm && sink) {
+            if (kNorm && sink && !sink_tanh) {
                 // the block's share of each token's sum of squares, added in feature order
                 __syncthreads();
                 if ((int)threadIdx.x < tok_n) {
@@ -594,7 +610,7 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
     ns_gemm_bf16_tc_tile(M_tok, &bn, &bm);
     if ((ep.row_partials || ep.sink_resid) && bn > 64)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: the norm epilogues take 64 tokens at most, not %d", M_tok);
-    if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || !ep.sink_partials))
+    if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || (!ep.sink_partials && !ep.sink_alpha)))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink needs %d features to be a multiple of %d, and all its tensors", N_feat, BM);
     if (ep.sink_resid && (ep.sink_ld % 4 || (uintptr_t)ep.sink_resid % 16))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink's residual rows must be 16-byte aligned (row stride %d floats)", ep.sink_ld);
@@ -663,6 +679,23 @@ NS_API int ns_gemm_bf16_tc_norm(const void* x, const void* w, void* out, int M_t
     ep.sink_partials = sink_partials;
     ep.sink_ld = sink_ld;
     return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
+}
+
+// A product whose output joins the residual stream and is followed by a norm that takes no statistics (64 tokens at most):
+// resid [M_tok, sink_ld] += product; sink_x [M_tok, sink_ld] = bf16(tanh(alpha * resid) * gain + bias).  `alpha` points at one
+// float in device memory; `bias` may be null.
+NS_API int ns_gemm_bf16_tc_dyt(const void* x, const void* w, int M_tok, int N_feat, int K, int ldx, int ldw, int splits,
+                               float* sink_resid, const float* sink_gain, const float* sink_bias, const float* sink_alpha,
+                               void* sink_x, int sink_ld, int* error_flag, cudaStream_t stream) {
+    if (!sink_resid || !sink_gain || !sink_alpha || !sink_x) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc_dyt: the stream, the gain, alpha and the output are needed");
+    GemmEpilogue ep = {};
+    ep.sink_resid = sink_resid;
+    ep.sink_gain = sink_gain;
+    ep.sink_bias = sink_bias;
+    ep.sink_alpha = sink_alpha;
+    ep.sink_x = (__nv_bfloat16*)sink_x;
+    ep.sink_ld = sink_ld;
+    return gemm_tc_host(x, w, nullptr, M_tok, N_feat, K, ldx, ldw, 0, 0, splits, ep, error_flag, stream);
 }
 
 // The packed q/k/v projection of an attention layer with the rotation and the cache write in its epilogue (64

@@ -264,6 +264,27 @@ class RowScaled:
         return self.x.dtype
 
 
+@dataclass
+class TanhSink:
+    """Where a product's output goes when the residual sum and a norm WITHOUT statistics that follow are folded into its epilogue:
+    `resid` [N, H] float32 is updated in place and tanh(alpha * resid) * gain + bias comes back complete, as a `Normed`."""
+
+    resid: torch.Tensor
+    gain: torch.Tensor
+    bias: torch.Tensor | None
+    alpha: torch.Tensor  # one float32 on the device
+    workspace: object
+
+
+@dataclass
+class Normed:
+    """Normed activations `x` [N, H] in the compute dtype that a product's epilogue has left, the stream already updated;
+    `gain` identifies the norm they stand for."""
+
+    x: torch.Tensor
+    gain: torch.Tensor
+
+
 def _tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     K = x.shape[1]
     return not (K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.stride(1) != 1 or w.stride(1) != 1
@@ -316,13 +337,25 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, sink: NormSink | None = None):
 
     `x` may be a `RowScaled` (its rows' scale is applied to the output).  With a `sink` that the product
     can fold in (`norm_fusion_ok`), nothing is written to `out`: the residual is updated and a `RowScaled`
-    for the norm that follows is returned; otherwise `out` is returned and the caller runs the norm.
+    for the norm that follows is returned; otherwise `out` is returned and the caller runs the norm.  A `TanhSink` (a norm
+    without statistics follows) likewise: the stream is updated and a `Normed` returned, or `out`.
 
     float32: the CUDA-core kernel (true fp32, k-ascending sums, independent of M).
     bfloat16: the tcgen05 kernel; operands that TMA cannot address (K or a row stride that is no
     multiple of 8) are a plain matrix product for cuBLAS, as the reference hands its `nn.Linear`
     calls to it (model/llama.py:175,184,195).  `out` may be bfloat16 or float32.
     """
+    if isinstance(sink, TanhSink):
+        if norm_fusion_ok(x.shape[0], x.dtype, w) and sink.resid.shape == (x.shape[0], w.shape[0]) and sink.resid.is_contiguous() \
+                and _tma_ok(x, w):
+            M, K = x.shape
+            N = w.shape[0]
+            normed = sink.workspace.get("sink_x", M, N, torch.bfloat16)
+            lib.call("ns_gemm_bf16_tc_dyt", x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), gemm_splits(M, N, K),
+                     sink.resid.data_ptr(), sink.gain.data_ptr(), _ptr(sink.bias), sink.alpha.data_ptr(), normed.data_ptr(), N,
+                     _tc(x.device).error.data_ptr(), _stream())
+            return Normed(normed, sink.gain)
+        sink = None  # the step does not fit: the plain product, and the caller's norm runs as a kernel of its own
     if isinstance(x, RowScaled) or (sink is not None and norm_fusion_ok(x.shape[0], x.dtype, w)
                                     and sink.resid.shape[1] == w.shape[0] and _tma_ok(x, w)):
         return _linear_norm(x, w, out, False, sink)

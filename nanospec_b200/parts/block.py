@@ -33,7 +33,9 @@ mixer's branch joins the stream through `ops.residual_add` and the feed-forward'
 When both sublayers offer their projections (`packs_projections`) the block runs TWO products a layer instead of four: one packed
 input projection [mixer's columns | feed-forward's] of h, and one output projection of the concatenated [heads' outputs |
 activations] by [W_o | W_down], whose float32 accumulator holds mixer(h) + feed_forward(h) before it is rounded once; the sublayers
-keep views of the packed matrices in place of their own (`adopt`), so weights are held once and replaced in place.
+keep views of the packed matrices in place of their own (`adopt`), so weights are held once and replaced in place.  In a step of up
+to 64 tokens the packed output product also adds its result to the stream and applies the NEXT block's norm in its epilogue, when
+that norm is elementwise (`elementwise_sink`): a decode layer is then five kernels and the tail of a convolution.
 """
 
 from __future__ import annotations
@@ -235,7 +237,12 @@ class ParallelBlock:
             mid = ctx.buffer("par_mid", self.w_out.shape[1])
             self.mixer.forward_projected(proj[:, :cm], ctx, lane, writes, mid[:, :om])
             self.feed_forward.forward_projected(proj[:, cm:], ctx, mid[:, om:])
-            return resid, ops.linear(mid, self.w_out, ctx.buffer("branch", resid.shape[1]))
+            # a step of a few tokens: the sum into the stream and the next block's norm in this product's epilogue
+            sink = None
+            nxt = getattr(follow, "norm_mixer", None) if isinstance(follow, ParallelBlock) else None
+            if nxt is not None and callable(getattr(nxt, "elementwise_sink", None)) and ops.norm_fusion_ok(ctx.n_tokens, self.w_out.dtype, self.w_out):
+                sink = nxt.elementwise_sink(resid, ctx)
+            return resid, ops.linear(mid, self.w_out, ctx.buffer("branch", resid.shape[1]), sink=sink)
         a = self.mixer.forward(h, ctx, lane, writes)
         if self.feed_forward is None:
             return resid, a

@@ -102,7 +102,8 @@ class LayerNorm(RMSNorm):
 class DynamicTanh(Part):
     """tanh(alpha * x) * gain + bias: a norm that takes no mean and no variance (one scalar `alpha` stored beside the gain and
     the bias), elementwise in float32 over the float32 stream and rounded once.  It is not a per-row scale, so it offers no `sink`
-    and is never folded into the products around it.  `add_norm` also takes a tuple of two pending branches (what a block that
+    (the folding of RMS norms); being elementwise, it offers `elementwise_sink` instead: a product of up to 64 tokens whose output
+    joins the stream right before this norm applies it in its epilogue.  `add_norm` also takes a tuple of two pending branches (what a block that
     runs its sublayers side by side leaves).  params: hidden, weight_name (default "weight"), bias_name (default weight_name +
     ".b"), alpha_name (default weight_name + ".alpha"); names follow the norm's prefix directly."""
 
@@ -130,10 +131,20 @@ class DynamicTanh(Part):
         self.bias = tensors[self.bias_name].contiguous()
         self.alpha = tensors[self.alpha_name].reshape(1).contiguous()
 
+    def elementwise_sink(self, resid: torch.Tensor, ctx: StepContext) -> ops.TanhSink:
+        """What a product needs to fold this norm and the residual sum before it into its epilogue (`ops.linear(..., sink=)`): the
+        norm is elementwise, so the product's epilogue leaves its result complete (`ops.Normed`), which `add_norm` hands on."""
+        return ops.TanhSink(resid, self.gain, self.bias, self.alpha, ctx.workspace)
+
     def add_norm(self, resid: torch.Tensor, pending, ctx: StepContext,
                  rows: torch.Tensor | None = None, out_name: str = "normed"):
         if isinstance(pending, ops.RowScaled):
             raise ValueError("a RowScaled reached a norm that cannot take it")
+        if isinstance(pending, ops.Normed):
+            # a product has added its output to the stream and applied this norm already
+            if pending.gain is not self.gain or rows is not None:
+                raise ValueError("a Normed reached a norm it was not made for")
+            return pending.x
         branches = pending if isinstance(pending, (tuple, list)) else (pending,)
         n = resid.shape[0] if rows is None else rows.numel()
         out = ctx.buffer(out_name, self.hidden, rows=n)

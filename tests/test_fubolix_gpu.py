@@ -421,6 +421,35 @@ def test_sublayers_with_products_of_their_own(dtype, tmp_path):
         close(run_cut(packed, 0, ids, cuts), want, dtype, f"packed products, portions {cuts or 'of one'}", noise)
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["eager", "graphs"])
+def test_the_next_norm_in_the_output_product(graphs, tmp_path):
+    """bfloat16, a width in multiples of 128, steps of up to 64 tokens: the packed output product adds its result to the stream and
+    applies the next layer's norm in its epilogue.  Portions of every size beside it, and generation through the engine."""
+    from nanospec_b200 import Engine, EngineConfig, SamplingParams
+    from nanospec_b200.ops import lib
+
+    cfg = config([windowed(dense(128), heads=4, kv_heads=2, dim=16), convolved(dense(64), dim=16, vdim=8), tempered(dense(128), dim=32, vdim=16),
+                  windowed(None, heads=2, kv_heads=1, dim=32, size=20), tempered(dense(64), dim=16, vdim=16)], width=128)
+    runner, w = make(tmp_path, cfg, seed=91, dtype=BF16, page=16, blocks=40)
+    ids = tokens(150, cfg["vocab"], 6)
+    want = plain.forward(cfg, w, ids)
+    noise = rounding(cfg, w, ids, want, samples=2)
+    lib.start_kernel_timing()
+    got = run_cut(runner, 0, ids, [64, 2, 30, 3])
+    seen = lib.stop_kernel_timing()
+    assert seen.get("ns_gemm_bf16_tc_dyt", (0, 0.0))[0] > 0, sorted(seen)
+    close(got, want, BF16, "the norm in the product's epilogue", noise)
+    close(run_cut(runner, 1, ids, [150]), want, BF16, "the same model, a whole prompt", noise)
+    eng = Engine(runner.model, EngineConfig(num_blocks=64, block_size=16, max_running=3, prefill_chunk=40, cuda_graphs=graphs, graph_buckets=(1, 2, 4)))
+    prompts = [tokens(n, cfg["vocab"], 60 + n) for n in (3, 70, 1, 17)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    for p, out in zip(prompts, outs):
+        z = plain.forward(cfg, w, p + out)
+        for j, tok in enumerate(out):
+            row = z[len(p) + j - 1]
+            assert float(row.max() - row[tok]) / float(z.std()) <= 0.1, f"token {j}"
+
+
 def test_layers_one_by_one(tmp_path):
     """The stream after every layer, in float32, against the plain statement's."""
     from nanospec_b200.engine.step import StepEntry
