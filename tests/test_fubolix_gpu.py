@@ -450,6 +450,23 @@ def test_the_next_norm_in_the_output_product(graphs, tmp_path):
             assert float(row.max() - row[tok]) / float(z.std()) <= 0.1, f"token {j}"
 
 
+@pytest.mark.parametrize("width", [36, 128], ids=["own products", "packed products"])
+def test_weights_replaced_in_place(width, tmp_path):
+    """`update_weights` on a bound model: the sublayers hold views of the block's packed matrices, and new tensors land there."""
+    from nanospec_b200.weights import update_weights
+
+    cfg = config([convolved(dense(64), dim=16, vdim=8), windowed(dense(32), heads=4, kv_heads=2, dim=16), tempered(None, dim=16, vdim=16)], width=width)
+    runner, w = make(tmp_path, cfg, seed=5)
+    assert (runner.model.blocks[0].w_in is not None) == (width == 128)
+    ids = tokens(40, cfg["vocab"], 9)
+    close(run_cut(runner, 0, ids, [17, 2]), plain.forward(cfg, w, ids), F32, "before")
+    w2 = random_weights(cfg, 6)
+    update_weights(runner.model, {k: v.clone() for k, v in w2.items()})
+    got = run_cut(runner, 1, ids, [17, 2])
+    close(got, plain.forward(cfg, w2, ids), F32, "after")
+    assert float(distance(got, plain.forward(cfg, w, ids)).max()) > 0.1
+
+
 def test_layers_one_by_one(tmp_path):
     """The stream after every layer, in float32, against the plain statement's."""
     from nanospec_b200.engine.step import StepEntry
