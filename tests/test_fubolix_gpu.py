@@ -467,6 +467,19 @@ def test_weights_replaced_in_place(width, tmp_path):
     assert float(distance(got, plain.forward(cfg, w, ids)).max()) > 0.1
 
 
+@pytest.mark.parametrize("packed", [False, True], ids=["own products", "packed products"])
+def test_float32_logits_do_not_depend_on_the_cut(packed, tmp_path):
+    """In float32 every sum runs in an order fixed per output element: whole, token by token and in portions give the same bits."""
+    cfg = config([windowed(dense(128), heads=4, kv_heads=2, dim=16), convolved(dense(64), dim=16, vdim=8), tempered(dense(128), dim=32, vdim=16)],
+                 width=128) if packed else full_config()
+    runner, _ = make(tmp_path, cfg, seed=3, page=4, blocks=80)
+    assert (runner.model.blocks[0].w_in is not None) == packed
+    ids = tokens(150, cfg["vocab"], 5)
+    whole = run_cut(runner, 0, ids, [150])
+    for i, cuts in enumerate(([], [2, 3, 2, 11, 5, 2], [64, 65, 1, 1, 17])):
+        assert torch.equal(run_cut(runner, i + 1, ids, cuts), whole), cuts
+
+
 def test_layers_one_by_one(tmp_path):
     """The stream after every layer, in float32, against the plain statement's."""
     from nanospec_b200.engine.step import StepEntry
